@@ -1,0 +1,154 @@
+// Shared device helpers and host-side plumbing of the b200ops launcher.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+
+#include "../../include/b200ops.h"
+
+namespace b200 {
+
+// ---------------------------------------------------------------------------
+// Host plumbing
+// ---------------------------------------------------------------------------
+
+struct Counters {
+  std::atomic<uint64_t> launches{0}, calls{0}, refusals{0}, cuda_errors{0};
+  std::atomic<int32_t> last_refusal{0};
+};
+Counters& counters();
+bool enabled();
+
+// Result bookkeeping for every entry point.
+int finish(int code);
+inline int refuse(int code) { return finish(code); }
+// After the last launch of an entry point: counts the kernels and the call.
+int launched(int kernels = 1);
+// After a launch that more work follows: 0 or -(cudaError_t); counts the kernels only.
+int check_launch(int kernels = 1);
+
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+inline int64_t round_up(int64_t a, int64_t b) { return ceil_div(a, b) * b; }
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+inline size_t dtype_size(int32_t dtype) { return dtype == B200_F32 ? 4 : 2; }
+inline bool valid_dtype(int32_t dtype) { return dtype == B200_F32 || dtype == B200_BF16; }
+
+struct DeviceInfo {
+  int device = -1;
+  int sm_count = 0;
+  int cc_major = 0, cc_minor = 0;
+  size_t smem_optin = 0;
+};
+// Properties of the current device (cached per device); sm_count == 0 if none.
+const DeviceInfo& device_info();
+
+// Device word kernels OR error bits into when a bounded wait runs out.
+int32_t* kernel_status_word();
+
+// ---------------------------------------------------------------------------
+// Device helpers
+// ---------------------------------------------------------------------------
+
+template <typename T>
+struct Elem;
+template <>
+struct Elem<float> {
+  static __device__ __forceinline__ float load(const float* p) { return *p; }
+  static __device__ __forceinline__ void store(float* p, float v) { *p = v; }
+  static constexpr int kVec = 4;  // elements per 16 bytes
+};
+template <>
+struct Elem<__nv_bfloat16> {
+  static __device__ __forceinline__ float load(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+  static constexpr int kVec = 8;
+};
+
+// 16-byte vector <-> float registers.
+__device__ __forceinline__ void unpack16(const uint4& raw, float (&v)[4]) {
+  v[0] = __uint_as_float(raw.x);
+  v[1] = __uint_as_float(raw.y);
+  v[2] = __uint_as_float(raw.z);
+  v[3] = __uint_as_float(raw.w);
+}
+__device__ __forceinline__ void unpack16(const uint4& raw, float (&v)[8]) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ uint4 pack16(const float (&v)[4]) {
+  return make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3]));
+}
+__device__ __forceinline__ uint4 pack16(const float (&v)[8]) {
+  return make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                    pack_bf16x2(v[6], v[7]));
+}
+
+// Streaming 16-byte accesses: data touched once should not displace reused lines in L1.
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p));
+  return r;
+}
+__device__ __forceinline__ uint4 ld_plain16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ void st_stream16(void* p, const uint4& v) {
+  asm volatile("st.global.L1::no_allocate.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+// NaN-propagating maximum, as torch.maximum / amax (and the reference's
+// aten_bridge/nan_minmax.py) behave: any NaN operand gives NaN.
+__device__ __forceinline__ float nan_max(float a, float b) { return (a != a) ? a : ((b != b) ? b : fmaxf(a, b)); }
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = nan_max(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Activations of fused epilogues, all in f32.
+__device__ __forceinline__ float apply_act(int act, float x, float alpha) {
+  switch (act) {
+    case B200_ACT_RELU:
+      return (x != x) ? x : fmaxf(x, 0.f);
+    case B200_ACT_GELU_ERF:
+      return 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
+    case B200_ACT_GELU_TANH: {
+      const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+      return 0.5f * x * (1.f + tanhf(u));
+    }
+    case B200_ACT_SIGMOID:
+      return 1.f / (1.f + __expf(-x));
+    case B200_ACT_TANH:
+      return tanhf(x);
+    case B200_ACT_SILU:
+      return x / (1.f + __expf(-x));
+    case B200_ACT_LEAKY_RELU:
+      return x > 0.f ? x : x * alpha;
+    default:
+      return x;
+  }
+}
+template <int ACT>
+__device__ __forceinline__ float apply_act_ct(float x, float alpha) {
+  return apply_act(ACT, x, alpha);
+}
+
+}  // namespace b200

@@ -1,0 +1,215 @@
+// b200_gemm: validation and kernel choice.
+//
+// Paths, in order of preference:
+//   tensor cores  bf16 operands whose rows TMA can describe (16-byte aligned bases
+//                 and pitches), plain ROW/COL layouts directly; the two VNNI layouts
+//                 of B through an unpack to K-contiguous [N, K] in the caller's workspace
+//   FFMA          everything else (f32, odd pitches, blocked layouts), exact f32
+// The choice mirrors the dispatcher of helion_mlir_utils/matmul.py:1446-1570
+// (bf16 -> fused kernel, f32 -> split-K / fused / blocked) with the CPU tile
+// heuristics replaced by the SM count; block_sizes arrive as tile_m/n/k hints.
+#include <cstdio>
+#include <cstring>
+
+#include "gemm_common.cuh"
+
+namespace b200 {
+
+int umma_supports(const b200_gemm_desc& d);
+int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* partials, cudaStream_t stream);
+int explain_gemm_umma(const b200_gemm_desc& d, char* buf, size_t len);
+int run_gemm_simt(const b200_gemm_desc& d, const GemmOperand& a, const GemmOperand& b, const GemmEpilogue& epi,
+                  int splits, float* workspace, cudaStream_t stream);
+
+namespace {
+
+struct Resolved {
+  GemmOperand a, b;
+  GemmEpilogue epi;
+  int64_t k_pad;        // K as the packed layouts pad it
+  int64_t n_pad;        // N as the packed B layout pads it
+  bool b_is_vnni;
+  size_t unpack_bytes;  // workspace for B unpacked to [n_pad, k_pad] bf16
+  size_t partial_bytes; // workspace for parallel split-K partials
+};
+
+int validate(const b200_gemm_desc* d, Resolved* r) {
+  if (!d) return B200_E_NULL;
+  if (!valid_dtype(d->dtype) || !valid_dtype(d->out_dtype) || !valid_dtype(d->vec_dtype)) return B200_E_DTYPE;
+  if (d->a_layout < 0 || d->a_layout > B200_LAYOUT_BLOCKED) return B200_E_ARG;
+  if (d->b_layout < 0 || d->b_layout > B200_LAYOUT_VNNI_PANELS) return B200_E_ARG;
+  if (d->epilogue < 0 || d->epilogue >= B200_ACT_COUNT_) return B200_E_ARG;
+  if (d->force_kernel < 0 || d->force_kernel > 2) return B200_E_ARG;
+  if (d->m < 0 || d->n < 0 || d->k < 0 || d->batch < 1) return B200_E_SHAPE;
+  if (d->split_k < 0 || d->split_k > 1024) return B200_E_ARG;
+  if ((d->b_layout == B200_LAYOUT_BLOCKED_VNNI || d->b_layout == B200_LAYOUT_VNNI_PANELS) && d->dtype != B200_BF16)
+    return B200_E_DTYPE;
+  if (d->b_layout == B200_LAYOUT_VNNI_PANELS && (d->b_panel <= 0 || d->b_panel % 32)) return B200_E_ARG;
+  if (d->m == 0 || d->n == 0) return 0;
+  if (!d->c || (d->k > 0 && (!d->a || !d->b))) return B200_E_NULL;
+  const size_t es = dtype_size(d->dtype);
+  if (!aligned(d->a, es) || !aligned(d->b, es) || !aligned(d->c, dtype_size(d->out_dtype))) return B200_E_ALIGN;
+  if (d->ldc < d->n) return B200_E_STRIDE;
+  if (d->a_layout == B200_LAYOUT_ROW && d->lda < d->k) return B200_E_STRIDE;
+  if (d->a_layout == B200_LAYOUT_COL && d->lda < d->m) return B200_E_STRIDE;
+  if (d->b_layout == B200_LAYOUT_ROW && d->ldb < d->n) return B200_E_STRIDE;
+  if (d->b_layout == B200_LAYOUT_COL && d->ldb < d->k) return B200_E_STRIDE;
+  const int64_t vec_n[3] = {d->bias_n, d->scale_n, d->shift_n};
+  const void* vec_p[3] = {d->bias, d->scale, d->shift};
+  for (int i = 0; i < 3; ++i)
+    if (vec_p[i] && vec_n[i] != 1 && vec_n[i] != d->n) return B200_E_SHAPE;
+
+  // C must not overlap A or B: CTAs read operands while others store results.
+  const uintptr_t c0 = reinterpret_cast<uintptr_t>(d->c);
+  const uintptr_t c1 = c0 + static_cast<uintptr_t>(((d->batch - 1) * d->stride_c + (d->m - 1) * d->ldc + d->n) *
+                                                   static_cast<int64_t>(dtype_size(d->out_dtype)));
+  const int64_t k32 = round_up(d->k, 32);
+  auto span = [&](const void* p, int64_t elems, int64_t stride) {
+    const uintptr_t p0 = reinterpret_cast<uintptr_t>(p);
+    const uintptr_t p1 = p0 + static_cast<uintptr_t>(((d->batch - 1) * stride + elems) * static_cast<int64_t>(es));
+    return p0 < c1 && c0 < p1;
+  };
+  int64_t a_elems, b_elems;
+  switch (d->a_layout) {
+    case B200_LAYOUT_ROW: a_elems = (d->m - 1) * d->lda + d->k; break;
+    case B200_LAYOUT_COL: a_elems = (d->k - 1) * d->lda + d->m; break;
+    default: a_elems = round_up(d->m, 32) * k32;
+  }
+  r->k_pad = k32;
+  r->n_pad = d->n;
+  switch (d->b_layout) {
+    case B200_LAYOUT_ROW: b_elems = (d->k - 1) * d->ldb + d->n; break;
+    case B200_LAYOUT_COL: b_elems = (d->n - 1) * d->ldb + d->k; break;
+    case B200_LAYOUT_VNNI_PANELS:
+      r->n_pad = round_up(d->n, d->b_panel);
+      b_elems = r->n_pad * k32;
+      break;
+    default:
+      r->n_pad = round_up(d->n, 32);
+      b_elems = r->n_pad * k32;
+  }
+  if (d->k > 0 && (span(d->a, a_elems, d->stride_a) || span(d->b, b_elems, d->stride_b))) return B200_E_ALIAS;
+
+  r->a = GemmOperand{d->a, d->a_layout, 0, d->lda, k32 / 32};
+  r->b = GemmOperand{d->b, d->b_layout, d->b_panel, d->ldb,
+                     d->b_layout == B200_LAYOUT_VNNI_PANELS ? k32 / 2 : k32 / 32};
+  r->epi = GemmEpilogue{d->bias,           d->scale,          d->shift,
+                        d->bias_n == 1,    d->scale_n == 1,   d->shift_n == 1,
+                        d->vec_dtype == B200_BF16, d->epilogue, d->alpha};
+  r->b_is_vnni = d->b_layout == B200_LAYOUT_BLOCKED_VNNI || d->b_layout == B200_LAYOUT_VNNI_PANELS;
+  r->unpack_bytes = r->b_is_vnni ? static_cast<size_t>(round_up(r->n_pad * k32 * 2, 256)) : 0;
+  r->partial_bytes =
+      d->split_k > 1 ? static_cast<size_t>(d->split_k) * d->batch * d->m * d->n * sizeof(float) : 0;
+  return 0;
+}
+
+// The descriptor the tensor-core kernel sees once a VNNI B has been unpacked.
+b200_gemm_desc unpacked_desc(const b200_gemm_desc& d, const Resolved& r, void* unpacked) {
+  b200_gemm_desc u = d;
+  u.b = unpacked;
+  u.b_layout = B200_LAYOUT_COL;
+  u.ldb = r.k_pad;
+  u.stride_b = r.n_pad * r.k_pad;
+  return u;
+}
+
+enum Path { kPathUmma, kPathUmmaUnpack, kPathSimt };
+
+// Chooses the path; `*why` gets the refusal of the tensor-core path when it is not taken.
+Path choose(const b200_gemm_desc& d, const Resolved& r, int* why) {
+  *why = 0;
+  if (d.force_kernel == 2) return kPathSimt;
+  if (d.k == 0) return kPathSimt;
+  if (r.b_is_vnni) {
+    if (d.a_layout > B200_LAYOUT_COL) {
+      *why = B200_E_ARG;
+      return kPathSimt;
+    }
+    if (d.batch != 1) {
+      *why = B200_E_SHAPE;
+      return kPathSimt;
+    }
+    if (!d.workspace || d.workspace_bytes < r.unpack_bytes || !aligned(d.workspace, 256)) {
+      *why = B200_E_WORKSPACE;
+      return kPathSimt;
+    }
+    b200_gemm_desc u = unpacked_desc(d, r, d.workspace);
+    *why = umma_supports(u);
+    return *why == 0 ? kPathUmmaUnpack : kPathSimt;
+  }
+  *why = umma_supports(d);
+  return *why == 0 ? kPathUmma : kPathSimt;
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" size_t b200_gemm_workspace_bytes(const b200_gemm_desc* desc) {
+  Resolved r{};
+  if (validate(desc, &r) != 0 || desc->m == 0 || desc->n == 0) return 0;
+  return r.unpack_bytes + r.partial_bytes;
+}
+
+extern "C" int b200_gemm(const b200_gemm_desc* desc, void* stream) {
+  if (!enabled()) return refuse(B200_E_DISABLED);
+  Resolved r{};
+  const int bad = validate(desc, &r);
+  if (bad) return refuse(bad);
+  const b200_gemm_desc& d = *desc;
+  if (d.m == 0 || d.n == 0) return finish(0);
+  if (device_info().sm_count == 0) return refuse(B200_E_DEVICE);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int why = 0;
+  const Path path = choose(d, r, &why);
+  if (path == kPathSimt && d.force_kernel == 1) return refuse(why ? why : B200_E_ARG);
+
+  // Workspace carve-up: [unpacked B][split-K partials].
+  uint8_t* ws = static_cast<uint8_t*>(d.workspace);
+  size_t ws_left = d.workspace ? d.workspace_bytes : 0;
+  void* unpacked = nullptr;
+  if (path == kPathUmmaUnpack) {
+    unpacked = ws;
+    ws += r.unpack_bytes;
+    ws_left -= r.unpack_bytes;
+  }
+  float* partials = nullptr;
+  if (d.split_k > 1 && ws_left >= r.partial_bytes && ws_left > 0 && aligned(ws, 16)) partials = reinterpret_cast<float*>(ws);
+
+  if (path == kPathSimt) return run_gemm_simt(d, r.a, r.b, r.epi, d.split_k, partials, s);
+
+  if (d.split_k > 1 && !partials && d.out_dtype != B200_F32) return refuse(B200_E_WORKSPACE);
+  if (path == kPathUmmaUnpack) {
+    const int kind =
+        d.b_layout == B200_LAYOUT_VNNI_PANELS ? B200_UNPACK_B_VNNI_PANELS_TO_NK : B200_UNPACK_B_VNNI_TO_NK;
+    const int rc = b200_pack(kind, B200_BF16, d.b, 0, 0, 0, unpacked, r.n_pad, r.k_pad, d.b_panel, stream);
+    if (rc != 0) return rc;
+    const b200_gemm_desc u = unpacked_desc(d, r, unpacked);
+    return run_gemm_umma(u, r.epi, partials, s);
+  }
+  return run_gemm_umma(d, r.epi, partials, s);
+}
+
+extern "C" int b200_gemm_explain(const b200_gemm_desc* desc, char* buf, size_t buf_len) {
+  if (!buf || buf_len == 0) return B200_E_NULL;
+  buf[0] = 0;
+  Resolved r{};
+  const int bad = validate(desc, &r);
+  if (bad) {
+    snprintf(buf, buf_len, "refused: %s", b200_strerror(bad));
+    return bad;
+  }
+  int why = 0;
+  const Path path = choose(*desc, r, &why);
+  if (path == kPathSimt) {
+    snprintf(buf, buf_len, "simt_ffma tile=128x128x16 (tensor-core path not taken: %s)",
+             desc->force_kernel == 2 ? "forced" : b200_strerror(why));
+    return desc->force_kernel == 1 ? (why ? why : B200_E_ARG) : 0;
+  }
+  const b200_gemm_desc u = path == kPathUmmaUnpack ? unpacked_desc(*desc, r, desc->workspace) : *desc;
+  char inner[200];
+  explain_gemm_umma(u, inner, sizeof inner);
+  snprintf(buf, buf_len, "%s%s", path == kPathUmmaUnpack ? "unpack_vnni + " : "", inner);
+  return 0;
+}

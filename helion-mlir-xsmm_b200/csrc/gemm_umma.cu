@@ -1,0 +1,660 @@
+// bf16 tensor-core GEMM for sm_100a: tcgen05.mma with the accumulator in tensor
+// memory, operands staged in shared memory by TMA, fused epilogue.
+//
+// One persistent CTA per SM, 6 warps:
+//   warps 0-3  epilogue: tcgen05.ld the 128 x BLOCK_N f32 accumulator (warp w owns
+//              TMEM lanes 32w..32w+31 = tile rows), + bias, * scale, + shift,
+//              activation, one rounding, stores to C
+//   warp 4     TMA producer: cp.async.bulk.tensor loads of the A and B stage
+//              (no cluster multicast: every CTA fetches its own tiles; reuse comes from L2)
+//   warp 5     MMA issuer: owns the TMEM allocation; one lane issues
+//              tcgen05.mma.cta_group::1.kind::f16 (M=128, N=BLOCK_N, K=16) and
+//              commits stage-empty / accumulator-full mbarriers
+// The accumulator is double buffered (2 x 256 TMEM columns), so the epilogue of
+// one tile overlaps the main loop of the next.
+//
+// Shared-memory operand tiles use the 128-byte swizzle shared by TMA and the
+// UMMA matrix descriptors. Per stage (64 K-elements):
+//   K-major operand  (K contiguous in memory): rows x 128 B, 8-row groups 1024 B apart
+//   MN-major operand (M or N contiguous): 64-element column chunks of 64 k-rows x 128 B
+//                    (8 KiB each), chunk j at j*8 KiB
+//
+// Every wait is bounded: a wait that runs out ORs a code into the device status
+// word, raises a CTA-wide abort flag, and all roles fall through to the common
+// teardown (TMEM is released, in-flight TMA stages are drained).
+#include <cuda.h>
+
+#include <cstdio>
+#include <mutex>
+
+#include "gemm_common.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kBlockM = 128;
+constexpr int kStageK = 64;  // bf16 elements per stage = one 128-byte swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 4;
+constexpr int kMaxStages = 8;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kAccStride = 256;  // TMEM columns between the two accumulators
+constexpr unsigned long long kWaitBudgetNs = 2000000000ull;
+
+// Status bits (also reported through b200_read_kernel_status).
+constexpr int kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueWait = 4, kErrDrainWait = 8;
+
+struct UmmaParams {
+  int32_t m, n, k, batch;
+  int32_t tiles_m, tiles_n;
+  int32_t splits;         // serial K splits per output tile
+  int32_t psplits;        // parallel K splits: each is a work item writing its own f32 partial
+  int64_t psplit_stride;  // elements of C between the partials of consecutive parallel splits
+  int32_t k_blocks;       // 64-wide K blocks per split
+  int32_t block_n;
+  int32_t stages;
+  int32_t a_kmajor, b_kmajor;
+  uint32_t idesc;
+  uint32_t a_stage_bytes, b_stage_bytes;
+  // matrix descriptor constants: high word and leading-byte-offset field
+  uint32_t a_desc_hi, b_desc_hi, a_desc_lbo, b_desc_lbo;
+  uint32_t a_kstep, b_kstep;  // descriptor start-address advance (16-byte units) per UMMA K step
+  GemmEpilogue epi;
+  void* c;
+  int64_t ldc, stride_c;
+  int32_t out_bf16;
+  int32_t vec_store;  // rows of C are 16-byte aligned
+  int32_t* status;
+};
+
+// --------------------------------------------------------------------------- PTX
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Waits for the phase of `parity` to complete. Gives up when the CTA aborted or
+// after kWaitBudgetNs; returns false then (and raises the abort with `code`).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
+                                          int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long start = global_ns();
+  for (uint32_t spin = 1;; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 63u) == 0) {
+      if (*abort_flag) return false;
+      if (global_ns() - start > kWaitBudgetNs) {
+        *abort_flag = 1;
+        if (status) atomicOr(status, code);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int32_t x, int32_t y,
+                                            int32_t z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t result_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(result_smem), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on `bar` once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_field, uint32_t hi) {
+  const uint32_t lo = ((smem_addr & 0x3FFFFu) >> 4) | (lbo_field << 16);
+  return (static_cast<uint64_t>(hi) << 32) | lo;
+}
+
+struct __align__(8) PipelineBarriers {
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// Output tile of a work item. Tiles of one batch are walked with N fastest so
+// that CTAs running together share rows of A and all of B in L2.
+struct Tile {
+  int32_t batch, m0, n0, ksplit;
+};
+__device__ __forceinline__ Tile tile_of(const UmmaParams& p, int64_t work) {
+  Tile t;
+  t.ksplit = static_cast<int32_t>(work % p.psplits);
+  work /= p.psplits;
+  const int64_t per_batch = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
+  t.batch = static_cast<int32_t>(work / per_batch);
+  const int64_t r = work - t.batch * per_batch;
+  t.m0 = static_cast<int32_t>(r / p.tiles_n) * kBlockM;
+  t.n0 = static_cast<int32_t>(r % p.tiles_n) * p.block_n;
+  return t;
+}
+
+__device__ __forceinline__ void activate32(int act, float alpha, float (&v)[32]) {
+  switch (act) {
+    case B200_ACT_IDENTITY:
+      break;
+    case B200_ACT_RELU:
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = apply_act(B200_ACT_RELU, v[j], alpha);
+      break;
+    case B200_ACT_GELU_ERF:
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = apply_act(B200_ACT_GELU_ERF, v[j], alpha);
+      break;
+    case B200_ACT_GELU_TANH:
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = apply_act(B200_ACT_GELU_TANH, v[j], alpha);
+      break;
+    case B200_ACT_SIGMOID:
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = apply_act(B200_ACT_SIGMOID, v[j], alpha);
+      break;
+    case B200_ACT_TANH:
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = apply_act(B200_ACT_TANH, v[j], alpha);
+      break;
+    case B200_ACT_SILU:
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = apply_act(B200_ACT_SILU, v[j], alpha);
+      break;
+    default:
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = apply_act(B200_ACT_LEAKY_RELU, v[j], alpha);
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_umma_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                          const UmmaParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: the 128-byte swizzle pattern repeats every 8 rows.
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t stage_bytes = p.a_stage_bytes + p.b_stage_bytes;
+  PipelineBarriers* bars = reinterpret_cast<PipelineBarriers*>(smem_aligned + static_cast<size_t>(p.stages) * stage_bytes);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t total_work = static_cast<int64_t>(p.batch) * p.tiles_m * p.tiles_n * p.psplits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&bars->full[s]), 1);
+      mbar_init(smem_u32(&bars->empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&bars->acc_full[a]), 1);
+      mbar_init(smem_u32(&bars->acc_empty[a]), kEpilogueWarps);
+    }
+    bars->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  if (warp == 5) {
+    tmem_alloc(smem_u32(&bars->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer
+    uint32_t it = 0;
+    bool ok = true;
+    for (int64_t work = blockIdx.x; work < total_work && ok; work += gridDim.x) {
+      const Tile t = tile_of(p, work);
+      for (int s = 0; s < p.splits && ok; ++s) {
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const uint32_t stage = it % p.stages, round = it / p.stages;
+          ok = mbar_wait(smem_u32(&bars->empty[stage]), (round & 1u) ^ 1u, abort_flag, p.status, kErrProducerWait);
+          ok = __all_sync(0xffffffffu, ok) != 0;
+          if (!ok) break;
+          if (lane == 0) {
+            const uint32_t full = smem_u32(&bars->full[stage]);
+            const uint32_t a_dst = smem_base + stage * stage_bytes;
+            const uint32_t b_dst = a_dst + p.a_stage_bytes;
+            const int32_t k0 = ((t.ksplit * p.splits + s) * p.k_blocks + kb) * kStageK;
+            mbar_expect_tx(full, stage_bytes);
+            if (p.a_kmajor) {
+              tma_load_3d(a_dst, &map_a, full, k0, t.m0, t.batch);
+            } else {
+              for (int j = 0; j < kBlockM / 64; ++j)
+                tma_load_3d(a_dst + j * 8192, &map_a, full, t.m0 + 64 * j, k0, t.batch);
+            }
+            if (p.b_kmajor) {
+              tma_load_3d(b_dst, &map_b, full, k0, t.n0, t.batch);
+            } else {
+              for (int j = 0; j < p.block_n / 64; ++j)
+                tma_load_3d(b_dst + j * 8192, &map_b, full, t.n0 + 64 * j, k0, t.batch);
+            }
+          }
+          __syncwarp();
+        }
+      }
+    }
+    // Drain: no stage this CTA armed may still be in flight when its shared memory is given up.
+    const uint32_t first = it > static_cast<uint32_t>(p.stages) ? it - p.stages : 0;
+    for (uint32_t j = first; j < it; ++j) {
+      const uint32_t stage = j % p.stages, round = j / p.stages;
+      int never = 0;
+      const bool drained = mbar_wait(smem_u32(&bars->full[stage]), round & 1u, &never, p.status, kErrDrainWait);
+      if (!__all_sync(0xffffffffu, drained)) break;
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer
+    uint32_t it = 0, phase = 0;
+    bool ok = true;
+    for (int64_t work = blockIdx.x; work < total_work && ok; work += gridDim.x) {
+      for (int s = 0; s < p.splits && ok; ++s, ++phase) {
+        const uint32_t acc = phase & 1u, acc_round = phase >> 1;
+        ok = mbar_wait(smem_u32(&bars->acc_empty[acc]), (acc_round & 1u) ^ 1u, abort_flag, p.status, kErrMmaWait);
+        ok = __all_sync(0xffffffffu, ok) != 0;
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kAccStride;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const uint32_t stage = it % p.stages, round = it / p.stages;
+          ok = mbar_wait(smem_u32(&bars->full[stage]), round & 1u, abort_flag, p.status, kErrMmaWait);
+          ok = __all_sync(0xffffffffu, ok) != 0;
+          if (!ok) break;
+          tc_fence_after();
+          if (lane == 0) {
+            const uint32_t a_addr = smem_base + stage * stage_bytes;
+            const uint32_t b_addr = a_addr + p.a_stage_bytes;
+            const uint64_t a_desc = make_desc(a_addr, p.a_desc_lbo, p.a_desc_hi);
+            const uint64_t b_desc = make_desc(b_addr, p.b_desc_lbo, p.b_desc_hi);
+#pragma unroll
+            for (int j = 0; j < kStageK / kUmmaK; ++j)
+              umma_bf16(d_tmem, a_desc + static_cast<uint64_t>(j * p.a_kstep),
+                        b_desc + static_cast<uint64_t>(j * p.b_kstep), p.idesc, (kb | j) != 0 ? 1u : 0u);
+            umma_commit(smem_u32(&bars->empty[stage]));
+            if (kb == p.k_blocks - 1) umma_commit(smem_u32(&bars->acc_full[acc]));
+          }
+          __syncwarp();
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    uint32_t phase = 0;
+    bool ok = true;
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    for (int64_t work = blockIdx.x; work < total_work && ok; work += gridDim.x) {
+      const Tile t = tile_of(p, work);
+      const int64_t row = static_cast<int64_t>(t.m0) + warp * 32 + lane;
+      const bool row_ok = row < p.m;
+      uint8_t* c_row = static_cast<uint8_t*>(p.c) +
+                       (static_cast<int64_t>(t.ksplit) * p.psplit_stride + static_cast<int64_t>(t.batch) * p.stride_c +
+                        row * p.ldc) *
+                           (p.out_bf16 ? 2 : 4);
+      for (int s = 0; s < p.splits && ok; ++s, ++phase) {
+        const uint32_t acc = phase & 1u, acc_round = phase >> 1;
+        ok = mbar_wait(smem_u32(&bars->acc_full[acc]), acc_round & 1u, abort_flag, p.status, kErrEpilogueWait);
+        ok = __all_sync(0xffffffffu, ok) != 0;
+        if (!ok) break;
+        tc_fence_after();
+        const bool last = s == p.splits - 1;
+        for (int c0 = 0; c0 < p.block_n; c0 += 32) {
+          uint32_t raw[32];
+          tmem_ld_32x32(tmem_base + lane_base + acc * kAccStride + c0, raw);
+          tmem_ld_wait();
+          const int64_t col0 = static_cast<int64_t>(t.n0) + c0;
+          if (!row_ok || col0 >= p.n) continue;
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+          const bool full_chunk = col0 + 32 <= p.n;
+          if (s > 0) {
+            // Serial split-K: partial sums live in C (f32) and are added in split order.
+            const float* prev = reinterpret_cast<const float*>(c_row) + col0;
+            if (full_chunk && p.vec_store) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float4 q = *reinterpret_cast<const float4*>(prev + 4 * j);
+                v[4 * j] += q.x;
+                v[4 * j + 1] += q.y;
+                v[4 * j + 2] += q.z;
+                v[4 * j + 3] += q.w;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.n) v[j] += prev[j];
+            }
+          }
+          if (last) {
+            if (p.epi.bias || p.epi.scale || p.epi.shift) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const int64_t col = (col0 + j < p.n) ? col0 + j : p.n - 1;
+                if (p.epi.bias) v[j] += load_vec(p.epi.bias, p.epi.bias_scalar ? 0 : col, p.epi.vec_bf16);
+                if (p.epi.scale) v[j] *= load_vec(p.epi.scale, p.epi.scale_scalar ? 0 : col, p.epi.vec_bf16);
+                if (p.epi.shift) v[j] += load_vec(p.epi.shift, p.epi.shift_scalar ? 0 : col, p.epi.vec_bf16);
+              }
+            }
+            activate32(p.epi.act, p.epi.alpha, v);
+          }
+          if (p.out_bf16) {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(c_row) + col0;
+            if (full_chunk && p.vec_store) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4 q;
+                q.x = pack_bf16x2(v[8 * j], v[8 * j + 1]);
+                q.y = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
+                q.z = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]);
+                q.w = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
+                *reinterpret_cast<uint4*>(dst + 8 * j) = q;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.n) dst[j] = __float2bfloat16_rn(v[j]);
+            }
+          } else {
+            float* dst = reinterpret_cast<float*>(c_row) + col0;
+            if (full_chunk && p.vec_store) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                *reinterpret_cast<float4*>(dst + 4 * j) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.n) dst[j] = v[j];
+            }
+          }
+        }
+        // This warp has read the whole accumulator: hand it back to the MMA warp.
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty[acc]));
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// --------------------------------------------------------------------------- host
+
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+  static EncodeTiled fn = [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &result) != cudaSuccess ||
+        result != cudaDriverEntryPointSuccess) {
+      cudaGetLastError();
+      sym = nullptr;
+    }
+    return reinterpret_cast<EncodeTiled>(sym);
+  }();
+  return fn;
+}
+
+// 3-D map over a row-major [batch][rows][cols] bf16 view with 128-byte swizzle.
+bool encode_map(CUtensorMap* map, const void* base, int64_t cols, int64_t rows, int64_t batch, int64_t ld,
+                int64_t batch_stride, uint32_t box_cols, uint32_t box_rows) {
+  EncodeTiled fn = encode_tiled();
+  if (!fn) return false;
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows),
+                              static_cast<cuuint64_t>(batch)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * 2, static_cast<cuuint64_t>(batch_stride) * 2};
+  const cuuint32_t box[3] = {box_cols, box_rows, 1};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+uint32_t make_idesc(int block_n, bool a_kmajor, bool b_kmajor) {
+  uint32_t d = 0;
+  d |= 1u << 4;   // D format f32
+  d |= 1u << 7;   // A format bf16
+  d |= 1u << 10;  // B format bf16
+  d |= (a_kmajor ? 0u : 1u) << 15;
+  d |= (b_kmajor ? 0u : 1u) << 16;
+  d |= static_cast<uint32_t>(block_n >> 3) << 17;
+  d |= static_cast<uint32_t>(kBlockM >> 4) << 24;
+  return d;
+}
+
+// High word of a matrix descriptor: stride byte offset, version 1, 128-byte swizzle.
+uint32_t desc_hi(uint32_t sbo_bytes) { return (sbo_bytes >> 4) | (1u << 14) | (2u << 29); }
+
+std::once_flag g_attr_once[64];
+
+}  // namespace
+
+// Whether the tensor-core path can take `d` (plain ROW/COL layouts of bf16).
+// The strides TMA needs: 16-byte aligned bases and row pitches.
+int umma_supports(const b200_gemm_desc& d) {
+  if (d.dtype != B200_BF16) return B200_E_DTYPE;
+  if (d.a_layout > B200_LAYOUT_COL || d.b_layout > B200_LAYOUT_COL) return B200_E_ARG;
+  if (!aligned(d.a, 16) || !aligned(d.b, 16)) return B200_E_ALIGN;
+  if (d.lda % 8 || d.ldb % 8 || (d.batch > 1 && (d.stride_a % 8 || d.stride_b % 8))) return B200_E_STRIDE;
+  if (d.m > INT32_MAX - 256 || d.n > INT32_MAX - 256 || d.k > INT32_MAX - 256 || d.batch > 65535)
+    return B200_E_SHAPE;
+  if (d.k < 1) return B200_E_SHAPE;
+  return 0;
+}
+
+struct UmmaPlan {
+  int block_n;
+  int stages;
+  int splits;   // serial
+  int psplits;  // parallel (workspace partials)
+  int k_blocks;
+  unsigned grid;
+  size_t smem;
+};
+
+UmmaPlan umma_plan(const b200_gemm_desc& d, int sm_count, bool parallel_splits) {
+  UmmaPlan plan;
+  const bool b_kmajor = d.b_layout == B200_LAYOUT_COL;
+  int bn = 256;
+  if (d.tile_n > 0) bn = static_cast<int>(round_up(d.tile_n, 64));
+  if (bn > 256) bn = 256;
+  // Narrow problems: no wider than N needs (MN-major B tiles come in 64-column chunks).
+  const int64_t n_cap = round_up(d.n, b_kmajor ? 16 : 64);
+  if (bn > n_cap) bn = static_cast<int>(n_cap);
+  // Too few tiles for the SMs: narrower tiles until every SM has work or 64 columns.
+  const int64_t psplit_factor = (parallel_splits && d.split_k > 1) ? d.split_k : 1;
+  while (d.tile_n <= 0 && bn > 64 && ceil_div(d.m, kBlockM) * ceil_div(d.n, bn) * d.batch * psplit_factor < sm_count)
+    bn /= 2;
+  if (!b_kmajor) bn = static_cast<int>(round_up(bn, 64));
+  plan.block_n = bn;
+  const int want_splits = d.split_k > 1 ? d.split_k : 1;
+  plan.psplits = parallel_splits ? want_splits : 1;
+  plan.splits = parallel_splits ? 1 : want_splits;
+  const int64_t k_blocks_total = ceil_div(d.k, kStageK);
+  plan.k_blocks = static_cast<int>(ceil_div(k_blocks_total, want_splits));
+  const size_t stage = static_cast<size_t>(kBlockM) * 128 + static_cast<size_t>(bn) * 128;
+  int stages = static_cast<int>((size_t(227) * 1024 - 2048) / stage);
+  if (stages > kMaxStages) stages = kMaxStages;
+  plan.stages = stages;
+  plan.smem = stage * stages + 1024 + sizeof(PipelineBarriers);
+  const int64_t work = ceil_div(d.m, kBlockM) * ceil_div(d.n, bn) * d.batch * plan.psplits;
+  plan.grid = static_cast<unsigned>(work < sm_count ? work : sm_count);
+  return plan;
+}
+
+// `partials`: NULL, or room for split_k * batch * m * n floats: the K splits then
+// run as parallel work items and the ordered reduction applies the epilogue.
+int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* partials, cudaStream_t stream) {
+  const DeviceInfo& dev = device_info();
+  if (dev.sm_count == 0) return refuse(B200_E_DEVICE);
+  const bool a_kmajor = d.a_layout == B200_LAYOUT_ROW;  // [M,K]: K contiguous
+  const bool b_kmajor = d.b_layout == B200_LAYOUT_COL;  // [N,K]: K contiguous
+  const bool parallel = partials != nullptr && d.split_k > 1;
+  const UmmaPlan plan = umma_plan(d, dev.sm_count, parallel);
+
+  CUtensorMap map_a, map_b;
+  bool ok;
+  if (a_kmajor)
+    ok = encode_map(&map_a, d.a, d.k, d.m, d.batch, d.lda, d.batch > 1 ? d.stride_a : d.lda * d.m, kStageK, kBlockM);
+  else
+    ok = encode_map(&map_a, d.a, d.m, d.k, d.batch, d.lda, d.batch > 1 ? d.stride_a : d.lda * d.k, 64, kStageK);
+  if (!ok) return refuse(B200_E_DEVICE);
+  if (b_kmajor)
+    ok = encode_map(&map_b, d.b, d.k, d.n, d.batch, d.ldb, d.batch > 1 ? d.stride_b : d.ldb * d.n, kStageK,
+                    plan.block_n);
+  else
+    ok = encode_map(&map_b, d.b, d.n, d.k, d.batch, d.ldb, d.batch > 1 ? d.stride_b : d.ldb * d.k, 64, kStageK);
+  if (!ok) return refuse(B200_E_DEVICE);
+
+  UmmaParams p{};
+  p.m = static_cast<int32_t>(d.m);
+  p.n = static_cast<int32_t>(d.n);
+  p.k = static_cast<int32_t>(d.k);
+  p.batch = static_cast<int32_t>(d.batch);
+  p.tiles_m = static_cast<int32_t>(ceil_div(d.m, kBlockM));
+  p.tiles_n = static_cast<int32_t>(ceil_div(d.n, plan.block_n));
+  p.splits = plan.splits;
+  p.psplits = plan.psplits;
+  p.k_blocks = plan.k_blocks;
+  p.block_n = plan.block_n;
+  p.stages = plan.stages;
+  p.a_kmajor = a_kmajor;
+  p.b_kmajor = b_kmajor;
+  p.idesc = make_idesc(plan.block_n, a_kmajor, b_kmajor);
+  p.a_stage_bytes = kBlockM * 128;
+  p.b_stage_bytes = static_cast<uint32_t>(plan.block_n) * 128;
+  // K-major: 8-row groups 1024 B apart, K step = 32 B inside the swizzled row.
+  // MN-major: 8-k-row groups 1024 B apart (SBO), 64-column chunks 8 KiB apart (LBO), K step = 16 rows = 2 KiB.
+  p.a_desc_hi = desc_hi(1024);
+  p.b_desc_hi = desc_hi(1024);
+  p.a_desc_lbo = a_kmajor ? 1u : (8192u >> 4);
+  p.b_desc_lbo = b_kmajor ? 1u : (8192u >> 4);
+  p.a_kstep = a_kmajor ? (32u >> 4) : (2048u >> 4);
+  p.b_kstep = b_kmajor ? (32u >> 4) : (2048u >> 4);
+  if (parallel) {
+    p.epi = GemmEpilogue{};
+    p.c = partials;
+    p.ldc = d.n;
+    p.stride_c = d.m * d.n;
+    p.psplit_stride = d.batch * d.m * d.n;
+    p.out_bf16 = 0;
+  } else {
+    p.epi = epi;
+    p.c = d.c;
+    p.ldc = d.ldc;
+    p.stride_c = d.stride_c;
+    p.out_bf16 = d.out_dtype == B200_BF16;
+  }
+  const size_t out_size = p.out_bf16 ? 2 : 4;
+  p.vec_store = aligned(p.c, 16) && (p.ldc * out_size) % 16 == 0 && (p.stride_c * out_size) % 16 == 0 &&
+                (p.psplit_stride * out_size) % 16 == 0;
+  p.status = kernel_status_word();
+
+  std::call_once(g_attr_once[dev.device], [] {
+    cudaFuncSetAttribute(gemm_umma_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  });
+  gemm_umma_bf16_kernel<<<plan.grid, kThreads, plan.smem, stream>>>(map_a, map_b, p);
+  if (!parallel) return launched();
+  const int rc = check_launch();
+  if (rc != 0) return finish(rc);
+  return launch_splitk_reduce(partials, plan.psplits, d.batch, d.m, d.n, d.c, d.out_dtype == B200_BF16, d.ldc,
+                              d.stride_c, epi, stream);
+}
+
+int explain_gemm_umma(const b200_gemm_desc& d, char* buf, size_t len) {
+  const DeviceInfo& dev = device_info();
+  const bool parallel = d.workspace != nullptr && d.split_k > 1;
+  const UmmaPlan plan = umma_plan(d, dev.sm_count > 0 ? dev.sm_count : 148, parallel);
+  snprintf(buf, len, "umma_bf16 tile=%dx%dx%d stages=%d serial_splits=%d parallel_splits=%d grid=%u smem=%zu", kBlockM,
+           plan.block_n, kStageK, plan.stages, plan.splits, plan.psplits, plan.grid, plan.smem);
+  return 0;
+}
+
+}  // namespace b200

@@ -1,0 +1,249 @@
+// Layout conversions for sm_100a: the packs of helion_mlir_utils/matmul.py
+// (pad_2d, pack_a_blocked[_t], pack_b_blocked[_t], pack_b_blocked_vnni[_t],
+// pack_b_vnni_t) and the inverse of the two VNNI layouts, used to hand VNNI
+// weights to the tensor-core GEMM as plain K-contiguous [N, K].
+//
+// All are bit-exact copies with zero fill past the source, so they are
+// HBM-bound: 2 bytes moved per byte packed. The forward packs map one thread to
+// `W` consecutive destination elements (16 bytes where the layout keeps that many
+// source elements adjacent); the VNNI unpacks are tiled transposes of 32-bit K
+// pairs through shared memory, 128-byte segments on both sides.
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+struct PackParams {
+  const void* src;
+  void* dst;
+  int64_t rows, cols, ld;      // source as stored
+  int64_t rows_pad, cols_pad;  // padded sizes in the source's orientation
+  int64_t total;               // destination elements
+  int32_t panel;
+};
+
+// Source coordinates (stored row, stored column) of destination element `o`.
+template <int KIND>
+__device__ __forceinline__ void source_of(const PackParams& p, int64_t o, int64_t& r, int64_t& c) {
+  if (KIND == B200_PACK_PAD_2D) {
+    r = o / p.cols_pad;
+    c = o - r * p.cols_pad;
+    return;
+  }
+  if (KIND == B200_PACK_B_VNNI_PANELS_T) {
+    // dst [Np/P][Kp/2][P][2]; src [N,K]: rows_pad = Np, cols_pad = Kp
+    const int64_t v = o & 1, nn = (o >> 1) % p.panel;
+    const int64_t rest = (o >> 1) / p.panel;
+    const int64_t pairs = p.cols_pad >> 1;
+    const int64_t cc = rest % pairs, q = rest / pairs;
+    r = q * p.panel + nn;
+    c = 2 * cc + v;
+    return;
+  }
+  const int64_t in_block = o & 1023, block = o >> 10;
+  int64_t major, kb, mn, k;  // block index along M or N, along K; offsets inside
+  if (KIND == B200_PACK_B_VNNI || KIND == B200_PACK_B_VNNI_T) {
+    const int64_t pbit = in_block & 1, nn = (in_block >> 1) & 31, rr = in_block >> 6;
+    k = 2 * rr + pbit;
+    mn = nn;
+  } else if (KIND == B200_PACK_A_BLOCKED || KIND == B200_PACK_A_BLOCKED_T) {
+    mn = in_block >> 5;  // [32 m][32 k]
+    k = in_block & 31;
+  } else {
+    k = in_block >> 5;  // [32 k][32 n]
+    mn = in_block & 31;
+  }
+  // K extent in the source's orientation.
+  const bool k_is_cols = (KIND == B200_PACK_A_BLOCKED || KIND == B200_PACK_B_BLOCKED_T || KIND == B200_PACK_B_VNNI_T);
+  const int64_t kblocks = (k_is_cols ? p.cols_pad : p.rows_pad) >> 5;
+  kb = block % kblocks;
+  major = block / kblocks;
+  const int64_t gm = major * 32 + mn, gk = kb * 32 + k;
+  if (k_is_cols) {
+    r = gm;
+    c = gk;
+  } else {
+    r = gk;
+    c = gm;
+  }
+}
+
+template <typename T, int KIND>
+__global__ void __launch_bounds__(256) pack_gather_kernel(const PackParams p) {
+  const T* __restrict__ src = static_cast<const T*>(p.src);
+  T* __restrict__ dst = static_cast<T*>(p.dst);
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t o = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; o < p.total; o += stride) {
+    int64_t r, c;
+    source_of<KIND>(p, o, r, c);
+    T value;
+    if (r < p.rows && c < p.cols) {
+      value = src[r * p.ld + c];
+    } else {
+      memset(&value, 0, sizeof(T));
+    }
+    dst[o] = value;
+  }
+}
+
+// Forward packs whose destination keeps W source elements adjacent: each thread
+// moves one 16-byte group when the whole group lies inside the source and both
+// sides are aligned, else element by element.
+template <typename T, int KIND>
+__global__ void __launch_bounds__(256) pack_rows_kernel(const PackParams p) {
+  constexpr int W = 16 / sizeof(T);
+  const T* __restrict__ src = static_cast<const T*>(p.src);
+  T* __restrict__ dst = static_cast<T*>(p.dst);
+  const int64_t groups = p.total / W;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t g = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g < groups; g += stride) {
+    int64_t r, c;
+    source_of<KIND>(p, g * W, r, c);
+    const T* s = src + r * p.ld + c;
+    if (r < p.rows && c + W <= p.cols && ((reinterpret_cast<uintptr_t>(s) & 15) == 0)) {
+      st_stream16(dst + g * W, ld_stream16(s));
+    } else {
+#pragma unroll
+      for (int j = 0; j < W; ++j) {
+        T value;
+        if (r < p.rows && c + j < p.cols) {
+          value = s[j];
+        } else {
+          memset(&value, 0, sizeof(T));
+        }
+        dst[g * W + j] = value;
+      }
+    }
+  }
+}
+
+// VNNI -> [Np, Kp] (K contiguous), as a transpose of 32-bit K pairs:
+//   blocks: src32[j][kb][r][nn]  -> dst32[32j+nn][16kb+r]
+//   panels: src32[q][c][nn]      -> dst32[qP+nn][c]
+// One CTA moves a 32(n) x 32(pairs) tile; grid.x walks pair tiles, grid.y n tiles.
+template <bool PANELS>
+__global__ void __launch_bounds__(256) unpack_vnni_kernel(const uint32_t* __restrict__ src, uint32_t* __restrict__ dst,
+                                                          int64_t n_pad, int64_t pairs, int32_t panel) {
+  __shared__ uint32_t tile[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  const int64_t n0 = static_cast<int64_t>(blockIdx.y) * 32, c0 = static_cast<int64_t>(blockIdx.x) * 32;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int64_t c = c0 + ty + 8 * i;  // pair index
+    const int64_t n = n0 + tx;
+    uint32_t value = 0;
+    if (c < pairs && n < n_pad) {
+      int64_t off;
+      if (PANELS) {
+        off = ((n / panel) * pairs + c) * panel + (n % panel);
+      } else {
+        off = (((n >> 5) * (pairs >> 4) + (c >> 4)) * 16 + (c & 15)) * 32 + (n & 31);
+      }
+      value = src[off];
+    }
+    tile[ty + 8 * i][tx] = value;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int64_t n = n0 + ty + 8 * i;
+    const int64_t c = c0 + tx;
+    if (c < pairs && n < n_pad) dst[n * pairs + c] = tile[tx][ty + 8 * i];
+  }
+}
+
+template <typename T, int KIND, bool ROWS>
+int launch_pack(const PackParams& p, cudaStream_t stream) {
+  const DeviceInfo& dev = device_info();
+  const int64_t items = ROWS ? p.total / (16 / sizeof(T)) : p.total;
+  const int64_t wanted = ceil_div(items, 256);
+  const int64_t resident = static_cast<int64_t>(dev.sm_count) * 16;
+  const unsigned grid = static_cast<unsigned>(wanted < resident ? wanted : resident);
+  if (ROWS)
+    pack_rows_kernel<T, KIND><<<grid, 256, 0, stream>>>(p);
+  else
+    pack_gather_kernel<T, KIND><<<grid, 256, 0, stream>>>(p);
+  return launched();
+}
+
+template <typename T>
+int run_pack(int kind, const PackParams& p, cudaStream_t stream) {
+  constexpr int W = 16 / sizeof(T);
+  const bool dst16 = aligned(p.dst, 16);
+  switch (kind) {
+    case B200_PACK_PAD_2D:
+      if (dst16 && p.cols_pad % W == 0) return launch_pack<T, B200_PACK_PAD_2D, true>(p, stream);
+      return launch_pack<T, B200_PACK_PAD_2D, false>(p, stream);
+    case B200_PACK_A_BLOCKED:  // 32 k adjacent in source rows
+      if (dst16) return launch_pack<T, B200_PACK_A_BLOCKED, true>(p, stream);
+      return launch_pack<T, B200_PACK_A_BLOCKED, false>(p, stream);
+    case B200_PACK_A_BLOCKED_T:
+      return launch_pack<T, B200_PACK_A_BLOCKED_T, false>(p, stream);
+    case B200_PACK_B_BLOCKED:  // 32 n adjacent in source rows
+      if (dst16) return launch_pack<T, B200_PACK_B_BLOCKED, true>(p, stream);
+      return launch_pack<T, B200_PACK_B_BLOCKED, false>(p, stream);
+    case B200_PACK_B_BLOCKED_T:
+      return launch_pack<T, B200_PACK_B_BLOCKED_T, false>(p, stream);
+    case B200_PACK_B_VNNI:
+      return launch_pack<T, B200_PACK_B_VNNI, false>(p, stream);
+    case B200_PACK_B_VNNI_T:
+      return launch_pack<T, B200_PACK_B_VNNI_T, false>(p, stream);
+    default:
+      return launch_pack<T, B200_PACK_B_VNNI_PANELS_T, false>(p, stream);
+  }
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_pack(int32_t kind, int32_t dtype, const void* src, int64_t rows, int64_t cols, int64_t ld,
+                         void* dst, int64_t rows_pad, int64_t cols_pad, int32_t panel, void* stream) {
+  if (!enabled()) return refuse(B200_E_DISABLED);
+  if (!valid_dtype(dtype)) return refuse(B200_E_DTYPE);
+  if (kind < 0 || kind >= B200_PACK_COUNT_) return refuse(B200_E_ARG);
+  if (rows < 0 || cols < 0 || rows_pad < 0 || cols_pad < 0) return refuse(B200_E_SHAPE);
+  if (rows_pad == 0 || cols_pad == 0) return finish(0);
+  if (!dst || (rows > 0 && cols > 0 && !src)) return refuse(B200_E_NULL);
+  if (ld < cols) return refuse(B200_E_STRIDE);
+  if (device_info().sm_count == 0) return refuse(B200_E_DEVICE);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+  if (kind == B200_UNPACK_B_VNNI_TO_NK || kind == B200_UNPACK_B_VNNI_PANELS_TO_NK) {
+    // rows_pad = Np, cols_pad = Kp of the [N, K] destination; the source is the packed tensor.
+    if (dtype != B200_BF16) return refuse(B200_E_DTYPE);
+    const bool panels = kind == B200_UNPACK_B_VNNI_PANELS_TO_NK;
+    if (cols_pad % 2) return refuse(B200_E_SHAPE);
+    if (panels ? (panel <= 0 || rows_pad % panel) : (rows_pad % 32 || cols_pad % 32)) return refuse(B200_E_SHAPE);
+    if (!aligned(src, 4) || !aligned(dst, 4)) return refuse(B200_E_ALIGN);
+    const int64_t pairs = cols_pad / 2;
+    const dim3 grid(static_cast<unsigned>(ceil_div(pairs, 32)), static_cast<unsigned>(ceil_div(rows_pad, 32)));
+    if (grid.y > 65535) return refuse(B200_E_SHAPE);
+    if (panels)
+      unpack_vnni_kernel<true><<<grid, 256, 0, s>>>(static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst),
+                                                    rows_pad, pairs, panel);
+    else
+      unpack_vnni_kernel<false><<<grid, 256, 0, s>>>(static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst),
+                                                     rows_pad, pairs, panel);
+    return launched();
+  }
+
+  if (rows_pad < rows || cols_pad < cols) return refuse(B200_E_SHAPE);
+  if (kind == B200_PACK_B_VNNI_PANELS_T) {
+    if (panel <= 0 || panel % 32 || rows_pad % panel || cols_pad % 2) return refuse(B200_E_SHAPE);
+  } else if (kind != B200_PACK_PAD_2D) {
+    if (rows_pad % 32 || cols_pad % 32) return refuse(B200_E_SHAPE);
+  }
+  PackParams p{};
+  p.src = src;
+  p.dst = dst;
+  p.rows = rows;
+  p.cols = cols;
+  p.ld = ld;
+  p.rows_pad = rows_pad;
+  p.cols_pad = cols_pad;
+  p.total = rows_pad * cols_pad;
+  p.panel = panel;
+  return dtype == B200_F32 ? run_pack<float>(kind, p, s) : run_pack<__nv_bfloat16>(kind, p, s);
+}

@@ -1,0 +1,272 @@
+// Row reductions (row_sum, row_dot, matvec) and column sums for sm_100a.
+//
+// All are one pass over x from HBM with f32 accumulation and a fixed summation
+// order (thread-strided partial sums, xor-shuffle tree, then the warps of a row
+// in index order), so two runs give the same bits. They replace
+// _row_sum_kernel, _row_dot_kernel, _matvec_kernel and _column_sum_kernel of
+// helion_mlir_utils/reduction.py.
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+struct ReduceParams {
+  const void* x;
+  const void* v;
+  void* out;
+  int64_t m, n, ld;
+  int32_t act;
+  float alpha;
+  int32_t tpr;
+};
+
+// KIND: 0 row_sum, 1 row_dot (v f32), 2 matvec (v of T)
+template <typename T, bool VEC, int KIND>
+__global__ void __launch_bounds__(256) row_reduce_kernel(const ReduceParams p) {
+  constexpr int EPV = VEC ? Elem<T>::kVec : 1;
+  __shared__ float red[8];
+  const int tpr = p.tpr;
+  const int rows_per_cta = blockDim.x / tpr;
+  const int row_in_cta = threadIdx.x / tpr;
+  const int t = threadIdx.x - row_in_cta * tpr;
+  const int lane = threadIdx.x & 31;
+  const int warps_per_row = tpr >> 5;
+  const int warp_in_row = t >> 5;
+  const T* x = reinterpret_cast<const T*>(p.x);
+  T* out = reinterpret_cast<T*>(p.out);
+  const float* vf = reinterpret_cast<const float*>(p.v);
+  const T* vt = reinterpret_cast<const T*>(p.v);
+
+  for (int64_t base = static_cast<int64_t>(blockIdx.x) * rows_per_cta; base < p.m;
+       base += static_cast<int64_t>(gridDim.x) * rows_per_cta) {
+    const int64_t row = base + row_in_cta;
+    const bool live = row < p.m;
+    const T* xr = x + row * p.ld;
+    float acc = 0.f;
+    if (live) {
+      for (int64_t col = static_cast<int64_t>(t) * EPV; col < p.n; col += static_cast<int64_t>(tpr) * EPV) {
+        float xv[EPV];
+        if constexpr (VEC) {
+          unpack16(ld_stream16(xr + col), xv);
+        } else {
+          xv[0] = Elem<T>::load(xr + col);
+        }
+        if (KIND == 0) {
+#pragma unroll
+          for (int j = 0; j < EPV; ++j) acc += xv[j];
+        } else if (KIND == 1) {
+#pragma unroll
+          for (int j = 0; j < EPV; ++j) acc += xv[j] * __ldg(vf + col + j);
+        } else {
+#pragma unroll
+          for (int j = 0; j < EPV; ++j) acc += xv[j] * Elem<T>::load(vt + col + j);
+        }
+      }
+    }
+    acc = warp_sum(acc);
+    if (warps_per_row > 1) {
+      if (lane == 0) red[row_in_cta * warps_per_row + warp_in_row] = acc;
+      __syncthreads();
+      acc = red[row_in_cta * warps_per_row];
+      for (int w = 1; w < warps_per_row; ++w) acc += red[row_in_cta * warps_per_row + w];
+      __syncthreads();
+    }
+    if (live && t == 0) Elem<T>::store(out + row, apply_act(p.act, acc, p.alpha));
+  }
+}
+
+template <typename T, bool VEC>
+int launch_row_reduce(int kind, const ReduceParams& p, unsigned grid, cudaStream_t stream) {
+  switch (kind) {
+    case B200_REDUCE_ROW_SUM:
+      row_reduce_kernel<T, VEC, 0><<<grid, 256, 0, stream>>>(p);
+      break;
+    case B200_REDUCE_ROW_DOT:
+      row_reduce_kernel<T, VEC, 1><<<grid, 256, 0, stream>>>(p);
+      break;
+    default:
+      row_reduce_kernel<T, VEC, 2><<<grid, 256, 0, stream>>>(p);
+  }
+  return launched();
+}
+
+template <typename T>
+int run_row_reduce(int kind, ReduceParams p, cudaStream_t stream) {
+  const DeviceInfo& dev = device_info();
+  if (dev.sm_count == 0) return refuse(B200_E_DEVICE);
+  const int kvec = Elem<T>::kVec;
+  const bool vec = (p.n % kvec == 0) && (p.ld % kvec == 0) && aligned(p.x, 16);
+  const int64_t units = vec ? p.n / kvec : p.n;
+  int tpr = 32;
+  while (tpr < 256 && static_cast<int64_t>(tpr) * 4 < units) tpr <<= 1;
+  p.tpr = tpr;
+  const int rows_per_cta = 256 / tpr;
+  const int64_t wanted = ceil_div(p.m, rows_per_cta);
+  const int64_t resident = static_cast<int64_t>(dev.sm_count) * 8;
+  const unsigned grid = static_cast<unsigned>(wanted < resident ? wanted : resident);
+  return vec ? launch_row_reduce<T, true>(kind, p, grid, stream) : launch_row_reduce<T, false>(kind, p, grid, stream);
+}
+
+// ---------------------------------------------------------------------------
+// Column sums: stage 1 sums a chunk of rows per CTA into partial[s][n] (or out
+// directly when there is one chunk); stage 2 adds the chunks in order.
+// ---------------------------------------------------------------------------
+
+constexpr int kColThreads = 128;
+constexpr int kColTargetCtas = 592;  // four CTAs per SM of a 148-SM part
+constexpr int kColMinRows = 64;
+
+struct ColPlan {
+  int cols_per_thread;
+  int64_t col_tiles;
+  int64_t chunks;
+  int64_t rows_per_chunk;
+};
+
+ColPlan column_plan(int64_t m, int64_t n, bool vec4) {
+  ColPlan plan;
+  plan.cols_per_thread = vec4 ? 4 : 1;
+  plan.col_tiles = ceil_div(n, static_cast<int64_t>(kColThreads) * plan.cols_per_thread);
+  int64_t chunks = kColTargetCtas / (plan.col_tiles > 0 ? plan.col_tiles : 1);
+  const int64_t max_chunks = m / kColMinRows;
+  if (chunks > max_chunks) chunks = max_chunks;
+  if (chunks < 1) chunks = 1;
+  plan.rows_per_chunk = ceil_div(m, chunks);
+  plan.chunks = ceil_div(m, plan.rows_per_chunk);
+  return plan;
+}
+
+template <typename T, int CPT>
+__global__ void __launch_bounds__(kColThreads) column_partial_kernel(const T* __restrict__ x, float* __restrict__ dst,
+                                                                     int64_t m, int64_t n, int64_t ld,
+                                                                     int64_t rows_per_chunk) {
+  const int64_t col = (static_cast<int64_t>(blockIdx.x) * kColThreads + threadIdx.x) * CPT;
+  if (col >= n) return;
+  const int64_t r0 = static_cast<int64_t>(blockIdx.y) * rows_per_chunk;
+  const int64_t r1 = (r0 + rows_per_chunk < m) ? r0 + rows_per_chunk : m;
+  float acc[CPT];
+#pragma unroll
+  for (int j = 0; j < CPT; ++j) acc[j] = 0.f;
+  const T* p = x + r0 * ld + col;
+#pragma unroll 4
+  for (int64_t r = r0; r < r1; ++r, p += ld) {
+    if (CPT == 4) {
+      if (sizeof(T) == 4) {
+        const float4 q = __ldg(reinterpret_cast<const float4*>(p));
+        acc[0] += q.x;
+        acc[1] += q.y;
+        acc[2] += q.z;
+        acc[3] += q.w;
+      } else {
+        const uint2 q = __ldg(reinterpret_cast<const uint2*>(p));
+        acc[0] += __uint_as_float(q.x << 16);
+        acc[1] += __uint_as_float(q.x & 0xffff0000u);
+        acc[2] += __uint_as_float(q.y << 16);
+        acc[3] += __uint_as_float(q.y & 0xffff0000u);
+      }
+    } else {
+      acc[0] += Elem<T>::load(p);
+    }
+  }
+  float* d = dst + static_cast<int64_t>(blockIdx.y) * n + col;
+#pragma unroll
+  for (int j = 0; j < CPT; ++j) d[j] = acc[j];
+}
+
+__global__ void column_final_kernel(const float* __restrict__ partial, float* __restrict__ out, int64_t n,
+                                    int64_t chunks) {
+  const int64_t col = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (col >= n) return;
+  float acc = partial[col];
+  for (int64_t s = 1; s < chunks; ++s) acc += partial[s * n + col];
+  out[col] = acc;
+}
+
+bool column_vec4(int32_t dtype, const void* x, int64_t n, int64_t ld) {
+  const size_t bytes = 4 * dtype_size(dtype);
+  return n % 4 == 0 && ld % 4 == 0 && aligned(x, bytes);
+}
+
+int column_sum_impl(int32_t dtype, const void* x, float* out, int64_t m, int64_t n, int64_t ld, void* workspace,
+                    size_t workspace_bytes, cudaStream_t stream) {
+  const bool vec4 = column_vec4(dtype, x, n, ld);
+  const ColPlan plan = column_plan(m, n, vec4);
+  float* stage1 = out;
+  if (plan.chunks > 1) {
+    const size_t need = static_cast<size_t>(plan.chunks) * n * sizeof(float);
+    if (!workspace || workspace_bytes < need) return refuse(B200_E_WORKSPACE);
+    if (!aligned(workspace, 16)) return refuse(B200_E_ALIGN);
+    stage1 = static_cast<float*>(workspace);
+  }
+  const dim3 grid(static_cast<unsigned>(plan.col_tiles), static_cast<unsigned>(plan.chunks));
+  if (dtype == B200_F32) {
+    const float* xs = static_cast<const float*>(x);
+    if (vec4)
+      column_partial_kernel<float, 4><<<grid, kColThreads, 0, stream>>>(xs, stage1, m, n, ld, plan.rows_per_chunk);
+    else
+      column_partial_kernel<float, 1><<<grid, kColThreads, 0, stream>>>(xs, stage1, m, n, ld, plan.rows_per_chunk);
+  } else {
+    const __nv_bfloat16* xs = static_cast<const __nv_bfloat16*>(x);
+    if (vec4)
+      column_partial_kernel<__nv_bfloat16, 4>
+          <<<grid, kColThreads, 0, stream>>>(xs, stage1, m, n, ld, plan.rows_per_chunk);
+    else
+      column_partial_kernel<__nv_bfloat16, 1>
+          <<<grid, kColThreads, 0, stream>>>(xs, stage1, m, n, ld, plan.rows_per_chunk);
+  }
+  if (plan.chunks > 1) {
+    const unsigned blocks = static_cast<unsigned>(ceil_div(n, 256));
+    column_final_kernel<<<blocks, 256, 0, stream>>>(stage1, out, n, plan.chunks);
+    return launched(2);
+  }
+  return launched(1);
+}
+
+size_t column_sum_workspace(int64_t m, int64_t n) {
+  if (m <= 0 || n <= 0) return 0;
+  // The vectorised plan has the fewest column tiles, hence the most chunks.
+  const ColPlan a = column_plan(m, n, true), b = column_plan(m, n, false);
+  const int64_t chunks = a.chunks > b.chunks ? a.chunks : b.chunks;
+  return chunks > 1 ? static_cast<size_t>(chunks) * n * sizeof(float) : 0;
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_row_reduce(int32_t kind, int32_t dtype, const void* x, const void* v, void* out, int64_t m,
+                               int64_t n, int64_t ld, int32_t act, float alpha, void* stream) {
+  if (!enabled()) return refuse(B200_E_DISABLED);
+  if (!valid_dtype(dtype)) return refuse(B200_E_DTYPE);
+  if (kind < 0 || kind > B200_REDUCE_MATVEC || act < 0 || act >= B200_ACT_COUNT_) return refuse(B200_E_ARG);
+  if (m < 0 || n < 0) return refuse(B200_E_SHAPE);
+  if (m == 0) return finish(0);
+  if (!out || (n > 0 && !x) || (kind != B200_REDUCE_ROW_SUM && n > 0 && !v)) return refuse(B200_E_NULL);
+  if (ld < n) return refuse(B200_E_STRIDE);
+  ReduceParams p{};
+  p.x = x;
+  p.v = v;
+  p.out = out;
+  p.m = m;
+  p.n = n;
+  p.ld = ld;
+  p.act = act;
+  p.alpha = alpha;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return dtype == B200_F32 ? run_row_reduce<float>(kind, p, s) : run_row_reduce<__nv_bfloat16>(kind, p, s);
+}
+
+extern "C" size_t b200_column_sum_workspace_bytes(int64_t m, int64_t n) { return column_sum_workspace(m, n); }
+
+extern "C" int b200_column_sum(int32_t dtype, const void* x, float* out, int64_t m, int64_t n, int64_t ld,
+                               void* workspace, size_t workspace_bytes, void* stream) {
+  if (!enabled()) return refuse(B200_E_DISABLED);
+  if (!valid_dtype(dtype)) return refuse(B200_E_DTYPE);
+  if (m < 1 || n < 0) return refuse(B200_E_SHAPE);
+  if (n == 0) return finish(0);
+  if (!x || !out) return refuse(B200_E_NULL);
+  if (ld < n) return refuse(B200_E_STRIDE);
+  if (device_info().sm_count == 0) return refuse(B200_E_DEVICE);
+  return column_sum_impl(dtype, x, out, m, n, ld, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}

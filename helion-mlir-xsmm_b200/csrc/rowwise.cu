@@ -1,0 +1,417 @@
+// Row-wise softmax / GroupNorm (LayerNorm) / RMSNorm for sm_100a.
+//
+// Bandwidth-bound kernels: every element of x is read from HBM once (one
+// 128-bit load where rows are 16-byte aligned), kept in registers while the row
+// statistics are reduced (warp shuffles, then shared memory across the warps of
+// a row), and written once. A row is owned by `tpr` threads (a power of two,
+// 32..1024); a CTA holds 256/tpr rows (at least one) and walks the rows with a
+// grid stride, so the grid is sized to the SM count times the resident CTAs.
+//
+// Arithmetic follows the bodies these kernels replace
+// (helion_mlir_utils/normalization.py): softmax = exp(x - rowmax) * (1 / sum)
+// (lines 52-72: multiply by the reciprocal), GroupNorm = two-pass mean then
+// biased variance of the centred values (lines 114-122), everything in f32 with
+// one rounding to the output type.
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+enum RowOp { kSoftmax = 0, kGroupNorm = 1, kRmsNorm = 2 };
+
+struct RowParams {
+  const void* x;
+  void* y;
+  int64_t rows;    // logical rows (M, or M*groups for GroupNorm)
+  int64_t n;       // row length
+  int64_t ld;      // elements between rows
+  int64_t groups;  // GroupNorm: rows per parameter period
+  const void* weight;
+  const void* bias;
+  const void* extra;
+  int32_t param_bf16;  // element type of weight/bias/extra
+  int32_t extra_op;
+  int32_t act;
+  float alpha;
+  float eps;
+  int32_t tpr;  // threads per row
+};
+
+__device__ __forceinline__ float load_param(const void* p, int64_t i, int bf16) {
+  return bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i])
+              : reinterpret_cast<const float*>(p)[i];
+}
+
+constexpr int kMaxWarpsPerRow = 32;
+
+// Reduces `v` over the `tpr` threads of a row. `scratch` has room for
+// rows_per_cta * warps_per_row floats. Every thread of the CTA must call this.
+template <bool IS_MAX>
+__device__ __forceinline__ float row_reduce(float v, float* scratch, int warps_per_row, int row_in_cta,
+                                            int warp_in_row, int lane) {
+  v = IS_MAX ? warp_max(v) : warp_sum(v);
+  if (warps_per_row == 1) return v;
+  if (lane == 0) scratch[row_in_cta * warps_per_row + warp_in_row] = v;
+  __syncthreads();
+  // Fixed order over the warps of the row: every thread gets the same bits.
+  float r = scratch[row_in_cta * warps_per_row];
+  for (int w = 1; w < warps_per_row; ++w) {
+    const float o = scratch[row_in_cta * warps_per_row + w];
+    r = IS_MAX ? nan_max(r, o) : r + o;
+  }
+  return r;
+}
+
+// VPT values per thread held in registers. VEC: 16-byte accesses (rows 16-byte
+// aligned and n a multiple of the vector width), else element accesses.
+// MAXT: the largest CTA the instantiation is launched with (register budget).
+template <typename T, bool VEC, int VPT, int OP, int MAXT>
+__global__ void __launch_bounds__(MAXT) rowwise_kernel(const RowParams p) {
+  constexpr int EPV = VEC ? Elem<T>::kVec : 1;
+  constexpr int NV = VPT / EPV;
+  static_assert(NV >= 1, "values per thread below one vector");
+  __shared__ float red_a[kMaxWarpsPerRow];
+  __shared__ float red_b[kMaxWarpsPerRow];
+
+  const int tpr = p.tpr;
+  const int rows_per_cta = blockDim.x / tpr;
+  const int row_in_cta = threadIdx.x / tpr;
+  const int t = threadIdx.x - row_in_cta * tpr;
+  const int lane = threadIdx.x & 31;
+  const int warps_per_row = tpr >> 5;
+  const int warp_in_row = t >> 5;
+  const T* __restrict__ x = reinterpret_cast<const T*>(p.x);
+  T* __restrict__ y = reinterpret_cast<T*>(p.y);
+  const int64_t n = p.n;
+  const float inv_n = 1.f / static_cast<float>(n);
+
+  for (int64_t base = static_cast<int64_t>(blockIdx.x) * rows_per_cta; base < p.rows;
+       base += static_cast<int64_t>(gridDim.x) * rows_per_cta) {
+    const int64_t row = base + row_in_cta;
+    const bool live = row < p.rows;
+    const T* xr = x + row * p.ld;
+    T* yr = y + row * p.ld;
+
+    float v[NV][EPV];
+    bool have[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int64_t col = (static_cast<int64_t>(i) * tpr + t) * EPV;
+      have[i] = live && col < n;
+      if constexpr (VEC) {
+        if (have[i]) {
+          float tmp[EPV];
+          unpack16(ld_stream16(xr + col), tmp);
+#pragma unroll
+          for (int j = 0; j < EPV; ++j) v[i][j] = tmp[j];
+        }
+      } else {
+        if (have[i]) v[i][0] = Elem<T>::load(xr + col);
+      }
+    }
+
+    if (OP == kSoftmax) {
+      float top = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+        if (have[i]) {
+#pragma unroll
+          for (int j = 0; j < EPV; ++j) top = nan_max(top, v[i][j]);
+        }
+      top = row_reduce<true>(top, red_a, warps_per_row, row_in_cta, warp_in_row, lane);
+      float total = 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+        if (have[i]) {
+#pragma unroll
+          for (int j = 0; j < EPV; ++j) {
+            v[i][j] = exp2f((v[i][j] - top) * 1.4426950408889634f);
+            total += v[i][j];
+          }
+        }
+      total = row_reduce<false>(total, red_b, warps_per_row, row_in_cta, warp_in_row, lane);
+      const float inv = 1.f / total;
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int j = 0; j < EPV; ++j) v[i][j] *= inv;
+    } else if (OP == kGroupNorm) {
+      float s = 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+        if (have[i]) {
+#pragma unroll
+          for (int j = 0; j < EPV; ++j) s += v[i][j];
+        }
+      s = row_reduce<false>(s, red_a, warps_per_row, row_in_cta, warp_in_row, lane);
+      const float mean = s * inv_n;
+      float q = 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+        if (have[i]) {
+#pragma unroll
+          for (int j = 0; j < EPV; ++j) {
+            v[i][j] -= mean;
+            q += v[i][j] * v[i][j];
+          }
+        }
+      q = row_reduce<false>(q, red_b, warps_per_row, row_in_cta, warp_in_row, lane);
+      const float rstd = rsqrtf(q * inv_n + p.eps);
+      const int64_t chan0 = (p.groups > 1 ? (row % p.groups) : 0) * n;
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+        if (have[i]) {
+          const int64_t col = (static_cast<int64_t>(i) * tpr + t) * EPV;
+#pragma unroll
+          for (int j = 0; j < EPV; ++j) {
+            const int64_t c = chan0 + col + j;
+            float r = v[i][j] * rstd;
+            if (p.weight) r *= load_param(p.weight, c, p.param_bf16);
+            if (p.bias) r += load_param(p.bias, c, p.param_bf16);
+            if (p.extra_op == B200_NORM_EXTRA_ADD) r += load_param(p.extra, c, p.param_bf16);
+            if (p.extra_op == B200_NORM_EXTRA_MUL) r *= load_param(p.extra, c, p.param_bf16);
+            v[i][j] = apply_act(p.act, r, p.alpha);
+          }
+        }
+    } else {  // kRmsNorm
+      float q = 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+        if (have[i]) {
+#pragma unroll
+          for (int j = 0; j < EPV; ++j) q += v[i][j] * v[i][j];
+        }
+      q = row_reduce<false>(q, red_a, warps_per_row, row_in_cta, warp_in_row, lane);
+      const float rstd = rsqrtf(q * inv_n + p.eps);
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+        if (have[i]) {
+          const int64_t col = (static_cast<int64_t>(i) * tpr + t) * EPV;
+#pragma unroll
+          for (int j = 0; j < EPV; ++j) {
+            float r = v[i][j] * rstd;
+            if (p.weight) r *= load_param(p.weight, col + j, p.param_bf16);
+            v[i][j] = r;
+          }
+        }
+      // red_b is untouched by this op: keep the two-barrier cadence the other
+      // ops have so the next row's first reduction cannot overtake readers.
+      if (warps_per_row > 1) __syncthreads();
+    }
+
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      if (!have[i]) continue;
+      const int64_t col = (static_cast<int64_t>(i) * tpr + t) * EPV;
+      if constexpr (VEC) {
+        float tmp[EPV];
+#pragma unroll
+        for (int j = 0; j < EPV; ++j) tmp[j] = v[i][j];
+        st_stream16(yr + col, pack16(tmp));
+      } else {
+        Elem<T>::store(yr + col, v[i][0]);
+      }
+    }
+  }
+}
+
+// Rows too long for registers: one CTA per row, several passes over the row
+// (the later passes hit L2 for rows up to tens of MB).
+template <typename T, int OP>
+__global__ void __launch_bounds__(1024) rowwise_long_kernel(const RowParams p) {
+  __shared__ float red_a[kMaxWarpsPerRow];
+  __shared__ float red_b[kMaxWarpsPerRow];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const T* x = reinterpret_cast<const T*>(p.x);
+  T* y = reinterpret_cast<T*>(p.y);
+  const int64_t n = p.n;
+  const float inv_n = 1.f / static_cast<float>(n);
+  for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
+    const T* xr = x + row * p.ld;
+    T* yr = y + row * p.ld;
+    if (OP == kSoftmax) {
+      float top = -INFINITY;
+      for (int64_t c = threadIdx.x; c < n; c += blockDim.x) top = nan_max(top, Elem<T>::load(xr + c));
+      top = row_reduce<true>(top, red_a, warps, 0, warp, lane);
+      float total = 0.f;
+      for (int64_t c = threadIdx.x; c < n; c += blockDim.x)
+        total += exp2f((Elem<T>::load(xr + c) - top) * 1.4426950408889634f);
+      total = row_reduce<false>(total, red_b, warps, 0, warp, lane);
+      const float inv = 1.f / total;
+      for (int64_t c = threadIdx.x; c < n; c += blockDim.x)
+        Elem<T>::store(yr + c, exp2f((Elem<T>::load(xr + c) - top) * 1.4426950408889634f) * inv);
+    } else if (OP == kGroupNorm) {
+      float s = 0.f;
+      for (int64_t c = threadIdx.x; c < n; c += blockDim.x) s += Elem<T>::load(xr + c);
+      s = row_reduce<false>(s, red_a, warps, 0, warp, lane);
+      const float mean = s * inv_n;
+      float q = 0.f;
+      for (int64_t c = threadIdx.x; c < n; c += blockDim.x) {
+        const float d = Elem<T>::load(xr + c) - mean;
+        q += d * d;
+      }
+      q = row_reduce<false>(q, red_b, warps, 0, warp, lane);
+      const float rstd = rsqrtf(q * inv_n + p.eps);
+      const int64_t chan0 = (p.groups > 1 ? (row % p.groups) : 0) * n;
+      for (int64_t c = threadIdx.x; c < n; c += blockDim.x) {
+        float r = (Elem<T>::load(xr + c) - mean) * rstd;
+        if (p.weight) r *= load_param(p.weight, chan0 + c, p.param_bf16);
+        if (p.bias) r += load_param(p.bias, chan0 + c, p.param_bf16);
+        if (p.extra_op == B200_NORM_EXTRA_ADD) r += load_param(p.extra, chan0 + c, p.param_bf16);
+        if (p.extra_op == B200_NORM_EXTRA_MUL) r *= load_param(p.extra, chan0 + c, p.param_bf16);
+        Elem<T>::store(yr + c, apply_act(p.act, r, p.alpha));
+      }
+    } else {
+      float q = 0.f;
+      for (int64_t c = threadIdx.x; c < n; c += blockDim.x) {
+        const float d = Elem<T>::load(xr + c);
+        q += d * d;
+      }
+      q = row_reduce<false>(q, red_a, warps, 0, warp, lane);
+      const float rstd = rsqrtf(q * inv_n + p.eps);
+      for (int64_t c = threadIdx.x; c < n; c += blockDim.x) {
+        float r = Elem<T>::load(xr + c) * rstd;
+        if (p.weight) r *= load_param(p.weight, c, p.param_bf16);
+        Elem<T>::store(yr + c, r);
+      }
+      __syncthreads();
+    }
+    // In-place rows: all reads of this row by this CTA are done (each thread
+    // re-reads only the columns it writes), so no extra barrier is needed.
+  }
+}
+
+template <typename T, bool VEC, int VPT, int OP, int MAXT>
+int launch_rowwise(const RowParams& p, int cta_threads, cudaStream_t stream) {
+  const int rows_per_cta = cta_threads / p.tpr;
+  int per_sm = 0;
+  auto kernel = rowwise_kernel<T, VEC, VPT, OP, MAXT>;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, cta_threads, 0) != cudaSuccess || per_sm < 1)
+    per_sm = 1;
+  const int64_t wanted = ceil_div(p.rows, rows_per_cta);
+  const int64_t resident = static_cast<int64_t>(device_info().sm_count) * per_sm;
+  const unsigned grid = static_cast<unsigned>(wanted < resident ? wanted : resident);
+  kernel<<<grid, cta_threads, 0, stream>>>(p);
+  return launched();
+}
+
+template <typename T, bool VEC, int OP>
+int dispatch_vpt(const RowParams& p, int vpt, int cta_threads, cudaStream_t stream) {
+  switch (vpt) {
+    case 8:
+      return launch_rowwise<T, VEC, 8, OP, 256>(p, cta_threads, stream);
+    case 16:
+      return launch_rowwise<T, VEC, 16, OP, 256>(p, cta_threads, stream);
+    default:
+      if (cta_threads > 256) return launch_rowwise<T, VEC, 32, OP, 1024>(p, cta_threads, stream);
+      return launch_rowwise<T, VEC, 32, OP, 256>(p, cta_threads, stream);
+  }
+}
+
+template <typename T, int OP>
+int run_rowwise(RowParams p, cudaStream_t stream) {
+  if (p.rows == 0 || p.n == 0) return finish(0);
+  const DeviceInfo& dev = device_info();
+  if (dev.sm_count == 0) return refuse(B200_E_DEVICE);
+  const int kvec = Elem<T>::kVec;
+  const bool vec = (p.n % kvec == 0) && (p.ld % kvec == 0) && aligned(p.x, 16) && aligned(p.y, 16);
+  const int64_t units = vec ? p.n / kvec : p.n;  // accesses per row
+  const int per_unit = vec ? kvec : 1;
+  // Threads per row: up to 256 at 16 values per thread, then 32 values per
+  // thread, then wider CTAs (which are held to 64 registers per thread).
+  const int units16 = 16 / per_unit > 0 ? 16 / per_unit : 1, units32 = 32 / per_unit;
+  int tpr = 32;
+  while (tpr < 256 && static_cast<int64_t>(tpr) * units16 < units) tpr <<= 1;
+  while (tpr < 1024 && static_cast<int64_t>(tpr) * units32 < units) tpr <<= 1;
+  const int64_t per_thread_units = ceil_div(units, tpr);
+  const int64_t vpt_needed = per_thread_units * per_unit;
+  if (vpt_needed > 32) {
+    auto kernel = rowwise_long_kernel<T, OP>;
+    const int64_t resident = static_cast<int64_t>(dev.sm_count) * 2;
+    const unsigned grid = static_cast<unsigned>(p.rows < resident ? p.rows : resident);
+    p.tpr = 1024;
+    kernel<<<grid, 1024, 0, stream>>>(p);
+    return launched();
+  }
+  const int vpt = vpt_needed <= 8 ? 8 : (vpt_needed <= 16 ? 16 : 32);
+  p.tpr = tpr;
+  const int cta_threads = tpr > 256 ? tpr : 256;
+  if (vec) return dispatch_vpt<T, true, OP>(p, vpt, cta_threads, stream);
+  return dispatch_vpt<T, false, OP>(p, vpt, cta_threads, stream);
+}
+
+template <int OP>
+int run_rowwise_dtype(int32_t dtype, const RowParams& p, cudaStream_t stream) {
+  if (dtype == B200_F32) return run_rowwise<float, OP>(p, stream);
+  return run_rowwise<__nv_bfloat16, OP>(p, stream);
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_softmax(int32_t dtype, const void* x, void* y, int64_t m, int64_t n, int64_t ld, void* stream) {
+  if (!enabled()) return refuse(B200_E_DISABLED);
+  if (!valid_dtype(dtype)) return refuse(B200_E_DTYPE);
+  if (m < 0 || n < 0) return refuse(B200_E_SHAPE);
+  if (m == 0 || n == 0) return finish(0);
+  if (!x || !y) return refuse(B200_E_NULL);
+  if (ld < n) return refuse(B200_E_STRIDE);
+  if (!aligned(x, dtype_size(dtype)) || !aligned(y, dtype_size(dtype))) return refuse(B200_E_ALIGN);
+  RowParams p{};
+  p.x = x;
+  p.y = y;
+  p.rows = m;
+  p.n = n;
+  p.ld = ld;
+  p.groups = 1;
+  return run_rowwise_dtype<kSoftmax>(dtype, p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200_group_norm(int32_t dtype, int32_t param_dtype, const void* x, void* y, int64_t m, int64_t groups,
+                               int64_t group_size, const void* weight, const void* bias, const void* extra,
+                               int32_t extra_op, int32_t act, float alpha, float eps, void* stream) {
+  if (!enabled()) return refuse(B200_E_DISABLED);
+  if (!valid_dtype(dtype) || !valid_dtype(param_dtype)) return refuse(B200_E_DTYPE);
+  if (m < 0 || groups < 1 || group_size < 0) return refuse(B200_E_SHAPE);
+  if (extra_op < 0 || extra_op > B200_NORM_EXTRA_MUL || act < 0 || act >= B200_ACT_COUNT_) return refuse(B200_E_ARG);
+  if (m == 0 || group_size == 0) return finish(0);
+  if (!x || !y || (extra_op != B200_NORM_EXTRA_NONE && !extra)) return refuse(B200_E_NULL);
+  RowParams p{};
+  p.x = x;
+  p.y = y;
+  p.rows = m * groups;
+  p.n = group_size;
+  p.ld = group_size;
+  p.groups = groups;
+  p.weight = weight;
+  p.bias = bias;
+  p.extra = extra;
+  p.param_bf16 = param_dtype == B200_BF16;
+  p.extra_op = extra_op;
+  p.act = act;
+  p.alpha = alpha;
+  p.eps = eps;
+  return run_rowwise_dtype<kGroupNorm>(dtype, p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200_rms_norm(int32_t dtype, int32_t param_dtype, const void* x, void* y, int64_t m, int64_t n,
+                             const void* weight, float eps, void* stream) {
+  if (!enabled()) return refuse(B200_E_DISABLED);
+  if (!valid_dtype(dtype) || !valid_dtype(param_dtype)) return refuse(B200_E_DTYPE);
+  if (m < 0 || n < 0) return refuse(B200_E_SHAPE);
+  if (m == 0 || n == 0) return finish(0);
+  if (!x || !y) return refuse(B200_E_NULL);
+  RowParams p{};
+  p.x = x;
+  p.y = y;
+  p.rows = m;
+  p.n = n;
+  p.ld = n;
+  p.groups = 1;
+  p.weight = weight;
+  p.param_bf16 = param_dtype == B200_BF16;
+  p.eps = eps;
+  return run_rowwise_dtype<kRmsNorm>(dtype, p, static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,137 @@
+"""Backend registration with Helion.
+
+Counterpart of ``helion_mlir_backend/inject.py`` of the reference:
+:func:`install` registers a compiler backend named ``"mlir"`` with Helion's
+backend registry and routes ``BoundKernel.compile_config`` of kernels that
+select it to this package (inject.py:22-56, 726-748). The reference's backend
+compiles the kernel body; this one *recognises* it: a body that is one of the
+``helion_mlir_utils`` operator bodies (or the canonical addmm tile loop) is
+mapped to its hand-written sm_100a kernel, with ``block_sizes`` passed on as tile
+hints, and any other body raises :class:`UnsupportedOperationError`.
+
+Helion is an optional dependency: without it :func:`install` returns ``False``
+(as inject.py:27-40 does on ``ImportError``) and the operator set still works
+through its own entry points.
+"""
+
+from __future__ import annotations
+
+import logging
+from typing import Callable
+
+from .driver import CONFIG_KEYS
+from .driver import warn_misspelt_config_keys
+from .errors import UnsupportedOperationError
+
+log = logging.getLogger(__name__)
+
+BACKEND_NAME = "mlir"
+PIPELINE_CONFIG_KEY = "mlir_pipeline"
+
+# body function (by code object) -> factory(block_sizes) -> native callable
+_RECOGNISED: dict[object, Callable[[tuple[int, ...] | None], Callable[..., object]]] = {}
+_installed = False
+
+
+def register_body(body: Callable[..., object], factory: Callable[[tuple[int, ...] | None], Callable[..., object]]) -> None:
+    """Declare ``factory(block_sizes)`` as the native implementation of a kernel body."""
+    _RECOGNISED[body.__code__] = factory
+
+
+def recognise(fn: Callable[..., object], config: object | None = None) -> Callable[..., object] | None:
+    """The native callable for kernel body ``fn`` under ``config``, or ``None``."""
+    code = getattr(fn, "__code__", None)
+    factory = _RECOGNISED.get(code)
+    if factory is None:
+        return None
+    block_sizes = None
+    if config is not None:
+        values = getattr(config, "config", config)
+        try:
+            block_sizes = tuple(int(v) for v in values.get("block_sizes", ()))  # type: ignore[union-attr]
+        except AttributeError:
+            block_sizes = None
+    return factory(block_sizes)
+
+
+def make_backend_class(base: type) -> type:
+    """The backend class registered with Helion (cf. ``MLIRBackend``,
+    ``_compiler/mlir/backend.py:44-122``): same name, same config keys, no
+    precompile, no power-of-two padding of factory tensors."""
+
+    class B200Backend(base):  # type: ignore[misc, valid-type]
+        @property
+        def name(self) -> str:
+            return BACKEND_NAME
+
+        @property
+        def experimental(self) -> bool:
+            return True
+
+        def supports_config_key(self, key: str) -> bool:
+            return key in CONFIG_KEYS
+
+        def supports_precompile(self) -> bool:
+            return False
+
+        @property
+        def pad_factory_tensors_to_power_of_2(self) -> bool:
+            return False
+
+        def classify_autotune_exception(self, err: BaseException) -> str | None:
+            return "warn" if isinstance(err, UnsupportedOperationError) else None
+
+    B200Backend.__name__ = "MLIRBackend"
+    return B200Backend
+
+
+def compile_config(bound_kernel: object, config: object, *, allow_print: bool = True) -> Callable[..., object]:
+    """What ``BoundKernel.compile_config`` returns for kernels on this backend
+    (cf. ``mlir_compile_config``, ``_compiler/mlir/driver.py:75-92``)."""
+    kernel = getattr(bound_kernel, "kernel", None)
+    fn = getattr(kernel, "fn", None)
+    name = getattr(fn, "__name__", "kernel")
+    warn_misspelt_config_keys(name, config)
+    native_op = recognise(fn, config) if fn is not None else None
+    if native_op is None:
+        raise UnsupportedOperationError(
+            f"{name}: the B200 backend runs hand-written kernels for the helion_mlir_utils operator set; "
+            "this kernel body matches none of them"
+        )
+    return native_op
+
+
+def install() -> bool:
+    """Register the backend with Helion. ``True`` when registration was applied."""
+    global _installed
+    if _installed:
+        return True
+    try:
+        from helion._compiler.backend import Backend
+        from helion._compiler.backend_registry import register_compiler_backend
+        from helion.runtime.kernel import BoundKernel
+    except ImportError as exc:
+        log.debug("Helion backend registration unavailable: %s", exc)
+        return False
+
+    backend_class = make_backend_class(Backend)
+    register_compiler_backend(backend_class)
+    original = BoundKernel.compile_config
+
+    def patched(self, config=None, *, allow_print: bool = True):  # type: ignore[no-untyped-def]
+        env = getattr(self, "env", None)
+        if getattr(getattr(env, "backend", None), "name", None) == BACKEND_NAME:
+            return compile_config(self, config, allow_print=allow_print)
+        return original(self, config, allow_print=allow_print)
+
+    BoundKernel.compile_config = patched
+    try:  # let Config accept `mlir_pipeline` (accepted and ignored: there is one pipeline)
+        from helion.runtime import config as helion_config
+
+        keys = getattr(helion_config, "VALID_KEYS", None)
+        if keys is not None and PIPELINE_CONFIG_KEY not in keys:
+            helion_config.VALID_KEYS = frozenset(keys) | {PIPELINE_CONFIG_KEY}
+    except ImportError:
+        pass
+    _installed = True
+    return True
