@@ -86,6 +86,8 @@ class _Lease:
 
 
 _max_bytes = 0
+_wrap_failed = False
+_limit_applied = False
 
 
 def _plain_dispatch() -> bool:
@@ -103,7 +105,12 @@ def _deterministic_fill() -> bool:
 
 
 def _takes(count: int, dtype: torch.dtype) -> bool:
-    return dtype in _DTYPES and MIN_BYTES <= dtype.itemsize * count <= _max_bytes and not _deterministic_fill()
+    return (
+        dtype in _DTYPES
+        and MIN_BYTES <= dtype.itemsize * count <= _max_bytes
+        and not _wrap_failed
+        and not _deterministic_fill()
+    )
 
 
 def _default_strides(sizes: tuple[int, ...]) -> tuple[int, ...]:
@@ -120,17 +127,28 @@ def _allocate(sizes: tuple[int, ...], count: int, dtype: torch.dtype, device: to
     if device.index is None:
         device = torch.device("cuda", torch.cuda.current_device())
     lib = native.module()
+    global _limit_applied
+    if not _limit_applied:  # the limit chosen at import, handed over once the library is loaded
+        _limit_applied = True
+        lib.b200_pool_set_limit(_max_bytes)
     with torch.cuda.device(device):
         code = lib.b200_pool_alloc(nbytes, native.stream_ptr(device), ctypes.byref(pointer), ctypes.byref(hit))
     if code != 0 or not pointer.value:
         return None  # torch's own attempt raises its error
     rounded = -(-nbytes // _GRANULE) * _GRANULE
-    lease = _Lease(pointer.value, rounded, device)
-    flat = torch.as_tensor(lease, device=device)
-    del lease  # the storage now owns the only reference
-    # Shaped in place on the pool's storage: a plain tensor, not a view of `flat`.
-    out = torch.empty(0, dtype=dtype, device=device)
-    out.set_(flat.untyped_storage(), 0, sizes, _default_strides(sizes))
+    lease = _Lease(pointer.value, rounded, device)  # its __del__ returns the block, also on failure below
+    try:
+        flat = torch.as_tensor(lease, device=device)
+        del lease  # the storage now owns the only reference
+        # Shaped in place on the pool's storage: a plain tensor, not a view of `flat`.
+        out = torch.empty(0, dtype=dtype, device=device)
+        out.set_(flat.untyped_storage(), 0, sizes, _default_strides(sizes))
+    except (RuntimeError, TypeError, ValueError) as exc:
+        global _wrap_failed
+        if not _wrap_failed:
+            _wrap_failed = True
+            warnings.warn(f"output pool: cannot wrap a device block as a tensor ({exc}); using torch.empty", stacklevel=3)
+        return None
     return out
 
 
@@ -169,12 +187,13 @@ def empty_like(x: torch.Tensor, *, dtype: torch.dtype | None = None) -> torch.Te
 def set_output_pool(max_bytes: int) -> None:
     """Keep at most ``max_bytes`` of free blocks; 0 turns the pool off and frees
     them. Tensors using a block are unaffected."""
-    global _max_bytes
+    global _max_bytes, _limit_applied
     _max_bytes = max(0, int(max_bytes))
     try:
         native.module().b200_pool_set_limit(_max_bytes)
+        _limit_applied = True
     except ImportError:
-        pass  # library not built yet: the limit is applied when it loads (see _apply_limit)
+        _limit_applied = False  # library not built yet: applied on first use
 
 
 def release() -> None:
@@ -216,8 +235,3 @@ def _default_max_bytes() -> int:
 
 
 _max_bytes = _default_max_bytes()
-
-
-def _apply_limit() -> None:
-    """Called once the library is loaded: hands it the limit chosen at import."""
-    native.module().b200_pool_set_limit(_max_bytes)

@@ -1,0 +1,201 @@
+"""The GEMM kernels against the CPU oracle on seeded inputs: the tcgen05 path in
+every operand orientation, ragged edges, K tails, fused epilogues, batches, both
+forms of split-K, and the five benchmark configurations at reduced size."""
+
+from __future__ import annotations
+
+import ctypes
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from helpers import cuda
+from oracle import checks
+from oracle import inputs
+from oracle import ops as ref
+
+pytestmark = pytest.mark.gpu
+BF16, F32 = torch.bfloat16, torch.float32
+
+
+@pytest.fixture(scope="module")
+def ops():
+    import helion_mlir_utils
+
+    return helion_mlir_utils
+
+
+@pytest.fixture(autouse=True)
+def no_kernel_gave_up():
+    """Every bounded wait in the kernels must have been satisfied."""
+    yield
+    from helion_mlir_backend import native
+
+    torch.cuda.synchronize()
+    assert native.kernel_status() == 0
+
+
+def rand(gen: torch.Generator, *shape: int, dtype=BF16, scale: float = 1.0) -> torch.Tensor:
+    return (torch.randn(*shape, generator=gen) * scale).to(dtype)
+
+
+def explain(ops, a, b, **kw) -> str:
+    return str(ops.matmul.explain(a, b, **kw))
+
+
+@pytest.mark.parametrize("trans_a", [False, True])
+@pytest.mark.parametrize("trans_b", [False, True])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 192), (200, 328, 136), (1000, 72, 520), (8, 16, 32)])
+def test_tensor_core_orientations(ops, shape, trans_a: bool, trans_b: bool) -> None:
+    m, n, k = shape
+    gen = torch.Generator().manual_seed(m * 31 + n * 7 + k + 2 * trans_a + trans_b)
+    a, b = rand(gen, m, k), rand(gen, k, n)
+    a_in = a.T.contiguous() if trans_a else a
+    b_in = b.T.contiguous() if trans_b else b
+    da, db = cuda(a_in, b_in)
+    assert "umma_bf16" in explain(ops, da, db, trans_a=trans_a, trans_b=trans_b)
+    out = ops.matmul(da, db, trans_a=trans_a, trans_b=trans_b)
+    checks.assert_parity(BF16, out.cpu(), ref.matmul(a, b), f"{shape} ta={trans_a} tb={trans_b}")
+    assert torch.equal(out, ops.matmul(da, db, trans_a=trans_a, trans_b=trans_b))  # run twice: same bits
+
+
+def test_tensor_core_matches_ffma_path(ops) -> None:
+    """Same operands through both kernels: f32 accumulation either way, one rounding."""
+    from helion_mlir_backend import native
+    from helion_mlir_utils import matmul as _  # noqa: F401
+    import importlib
+
+    mm = importlib.import_module("helion_mlir_utils.matmul")
+    gen = torch.Generator().manual_seed(5)
+    a, b = cuda(rand(gen, 384, 320), rand(gen, 320, 256))
+    fast = ops.matmul(a, b, out_dtype=F32)
+    plan = mm._plan_gemm(a=a, m=384, n=256, k=320, a_layout=native.LAYOUT_ROW, b_layout=native.LAYOUT_ROW, lda=320,
+                         ldb=256, bias=None, scale=None, shift=None, epilogue=ops.identity_epilogue, out_dtype=F32,
+                         force_kernel=2)
+    slow = plan.run(a, b)
+    assert "simt_ffma" in str(plan.explain(a, b))
+    assert checks.rel_frobenius(fast, slow) < 2e-6
+
+
+@pytest.mark.parametrize("act", ["relu", "gelu", "gelu_tanh", "sigmoid", "tanh", "silu", "leaky", "unfused"])
+def test_fused_epilogues(ops, act: str) -> None:
+    gen = torch.Generator().manual_seed(11)
+    m, n, k = 300, 264, 128
+    x, w = rand(gen, m, k), rand(gen, n, k, scale=0.125)
+    bias, scale, shift = rand(gen, n, scale=0.5), (1 + 0.1 * torch.randn(n, generator=gen)).to(BF16), rand(gen, 1, scale=0.1)
+    fn = {
+        "relu": torch.relu, "gelu": F.gelu, "gelu_tanh": ops.gelu_tanh, "sigmoid": torch.sigmoid, "tanh": torch.tanh,
+        "silu": F.silu, "leaky": ops.leaky_relu_epilogue(0.2), "unfused": lambda t: t * torch.sigmoid(1.5 * t),
+    }[act]
+    out = ops.matmul(*cuda(x, w), trans_b=True, bias=cuda(bias), scale=cuda(scale), shift=cuda(shift), epilogue=fn)
+    expect = ref.matmul(x, w, trans_b=True, bias=bias, scale=scale, shift=shift, epilogue=fn)
+    checks.assert_parity(BF16, out.cpu(), expect, act)
+    assert out.dtype == BF16
+
+
+def test_output_type_and_f32_vectors(ops) -> None:
+    gen = torch.Generator().manual_seed(12)
+    x, w = rand(gen, 130, 64), rand(gen, 96, 64)
+    bias = torch.randn(96, generator=gen)  # f32 bias with bf16 operands
+    out = ops.matmul(*cuda(x, w), trans_b=True, bias=cuda(bias), out_dtype=F32)
+    assert out.dtype == F32
+    assert checks.rel_frobenius(out.cpu(), ref.matmul(x, w, trans_b=True, bias=bias, out_dtype=F32)) < 1e-5
+
+
+def test_bmm_and_split_k(ops) -> None:
+    gen = torch.Generator().manual_seed(13)
+    a, b = rand(gen, 6, 256, 512), rand(gen, 6, 512, 128)
+    da, db = cuda(a, b)
+    checks.assert_parity(BF16, ops.bmm(da, db).cpu(), ref.bmm(a, b), "bmm")
+    serial = ops.bmm(da, db, split_k=4, out_dtype=F32)
+    assert serial.dtype == F32
+    assert checks.rel_frobenius(serial.cpu(), ref.bmm(a, b, split_k=4, out_dtype=F32)) < 1e-5
+    assert torch.equal(serial, ops.bmm(da, db, split_k=4, out_dtype=F32))  # ordered: same bits every run
+    rounded = ops.bmm(da, db, split_k=4)  # bf16 result: partial-sum workspace + ordered reduction
+    checks.assert_parity(BF16, rounded.cpu(), ref.bmm(a, b, split_k=4), "bmm split bf16")
+    # parallel split-K chosen automatically: few tiles, deep K
+    a2, b2 = rand(gen, 128, 8192), rand(gen, 8192, 128)
+    text = explain(ops, *cuda(a2, b2))
+    out = ops.matmul(*cuda(a2, b2))
+    checks.assert_parity(BF16, out.cpu(), ref.matmul(a2, b2), "auto split " + text)
+    with pytest.raises(RuntimeError, match="batch2"):
+        ops.bmm(da, db.transpose(1, 2).contiguous())
+
+
+def test_f32_paths(ops) -> None:
+    gen = torch.Generator().manual_seed(14)
+    for m, n, k in [(1024 // 4, 1024 // 4, 1024 // 4), (70, 45, 50), (1, 1, 1), (33, 129, 7)]:
+        a, b = rand(gen, m, k, dtype=F32), rand(gen, k, n, dtype=F32)
+        out = ops.matmul(*cuda(a, b), block_sizes=(64, 64, 64))
+        assert checks.rel_frobenius(out.cpu(), ref.matmul(a, b)) < 1e-5
+    a, b = rand(gen, 3, 40, 24, dtype=F32), rand(gen, 3, 24, 56, dtype=F32)
+    assert checks.rel_frobenius(ops.bmm(*cuda(a, b)).cpu(), ref.bmm(a, b)) < 1e-5
+    empty = ops.matmul(torch.zeros(0, 8, device="cuda"), torch.zeros(8, 4, device="cuda"))
+    assert empty.shape == (0, 4)
+    zero_k = ops.matmul(torch.zeros(5, 0, device="cuda"), torch.zeros(0, 4, device="cuda"))
+    assert torch.equal(zero_k.cpu(), torch.zeros(5, 4))
+
+
+def test_blocked_operands(ops) -> None:
+    gen = torch.Generator().manual_seed(15)
+    m, n, k = 100, 90, 70
+    a, b = rand(gen, m, k), rand(gen, k, n)
+    bias = rand(gen, n)
+    a4, b4, b5 = ref.pack_a_blocked(a), ref.pack_b_blocked(b), ref.pack_b_blocked_vnni(b)
+    expect = ref.matmul(a, b, bias=bias, epilogue=torch.relu, out_dtype=F32)
+    for packed in (b4, b5):
+        out = ops.matmul_blocked(*cuda(a4, packed), m, n, k, bias=cuda(bias), epilogue=torch.relu, out_dtype=F32)
+        assert out.shape == (m, n) and out.dtype == F32
+        assert checks.rel_frobenius(out.cpu(), expect) < 1e-5
+    out = ops.matmul_blocked(*cuda(a4, b4), m, n, k)
+    checks.assert_parity(BF16, out.cpu(), ref.matmul_blocked(a4, b4, m, n), "blocked bf16")
+
+
+def test_benchmark_configurations_reduced(ops) -> None:
+    """C1..C5 of the baseline at sizes the oracle finishes in seconds."""
+    c1 = inputs.c1_f32_matmul(256)
+    out = ops.matmul(*cuda(c1["a"], c1["b"]), block_sizes=[64, 64, 64])
+    assert checks.rel_frobenius(out.cpu(), ref.matmul(c1["a"], c1["b"])) < 1e-5
+    c2 = inputs.c2_linear(m=1024, n=512, k=4096)
+    out = ops.matmul(*cuda(c2["x"], c2["w"]), trans_b=True, bias=cuda(c2["b"]), epilogue=F.gelu)
+    checks.assert_parity(BF16, out.cpu(), ref.linear(c2["x"], c2["w"], c2["b"], F.gelu), "C2")
+    c3 = inputs.c3_blocked(512)
+    a4, b5 = ref.pack_a_blocked(c3["a"]), ref.pack_b_blocked_vnni(c3["b"])
+    out = ops.matmul_blocked(*cuda(a4, b5), 512, 512, 512, out_dtype=F32)
+    assert checks.rel_frobenius(out.cpu(), ref.matmul(c3["a"], c3["b"], out_dtype=F32)) < 1e-5
+    c5 = inputs.c5_split_k_bmm(batch=4, m=256, n=256, k=4096)
+    out = ops.bmm(*cuda(c5["a"], c5["b"]), split_k=8, out_dtype=F32)
+    assert checks.rel_frobenius(out.cpu(), ref.bmm(c5["a"], c5["b"], split_k=8, out_dtype=F32)) < 1e-5
+
+
+def test_full_size_properties(ops) -> None:
+    """Size-independent checks at the benchmark's full C2 size: linearity in x and
+    agreement of sampled rows with the oracle."""
+    c2 = inputs.c2_linear()
+    x, w, b = cuda(c2["x"], c2["w"], c2["b"])
+    y = ops.matmul(x, w, trans_b=True, bias=b, epilogue=F.gelu)
+    rows = torch.tensor([0, 1, 127, 128, 4095, 4096, 8191])
+    expect = ref.linear(c2["x"][rows], c2["w"], c2["b"], F.gelu)
+    checks.assert_parity(BF16, y.cpu()[rows], expect, "C2 sampled rows")
+    plain = ops.matmul(x, w, trans_b=True, out_dtype=F32)
+    doubled = ops.matmul(x * 2, w, trans_b=True, out_dtype=F32)
+    assert torch.equal(doubled, plain * 2)  # scaling by 2 is exact in bf16 and f32
+
+
+def test_c_abi_refuses_what_it_cannot_run(ops) -> None:
+    from helion_mlir_backend import native
+
+    lib = native.module()
+    a = torch.zeros(64, 64, device="cuda", dtype=BF16)
+    desc = native.GemmDesc()
+    desc.dtype = desc.out_dtype = desc.vec_dtype = native.BF16
+    desc.m = desc.n = desc.k = 64
+    desc.batch = 1
+    desc.lda = desc.ldb = desc.ldc = 64
+    desc.a = desc.b = a.data_ptr()
+    desc.c = a.data_ptr()  # output aliases an input
+    assert lib.b200_gemm(ctypes.byref(desc), native.stream_ptr(a.device)) == 5
+    desc.c = torch.zeros(64, 64, device="cuda", dtype=BF16).data_ptr()
+    desc.ldc = 32
+    assert lib.b200_gemm(ctypes.byref(desc), native.stream_ptr(a.device)) == 3

@@ -1,0 +1,179 @@
+"""Row-wise kernels, reductions and element-wise kernels against the CPU oracle:
+ragged and unaligned rows, one column, long rows, NaN/inf rows, in-place,
+both dtypes, and the C4 configuration."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from helpers import bits
+from helpers import cuda
+from oracle import checks
+from oracle import inputs
+from oracle import ops as ref
+
+pytestmark = pytest.mark.gpu
+BF16, F32 = torch.bfloat16, torch.float32
+SHAPES = [(32, 128), (64, 256), (16, 129), (33, 257), (2, 65), (1, 127), (5, 2), (7, 1), (3, 4096), (9, 4100),
+          (4, 8192), (3, 10000), (2, 40000), (300, 64), (1000, 24)]
+
+
+@pytest.fixture(scope="module")
+def ops():
+    import helion_mlir_utils
+
+    return helion_mlir_utils
+
+
+def tol(dtype) -> float:
+    return 1e-6 if dtype == F32 else 1e-2
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_softmax(ops, shape, dtype) -> None:
+    gen = torch.Generator().manual_seed(shape[0] * 131 + shape[1])
+    x = (torch.randn(*shape, generator=gen) * 3).to(dtype)
+    out = ops.softmax(cuda(x))
+    assert checks.max_norm_rel(out.cpu(), ref.softmax(x)) < tol(dtype)
+    y = cuda(x).clone()
+    pointer = y.data_ptr()
+    in_place = ops.softmax(y, in_place=True)
+    assert in_place.data_ptr() == pointer and torch.equal(bits(in_place), bits(out))
+
+
+def test_softmax_special_rows(ops) -> None:
+    x = torch.randn(6, 300)
+    x[0, 5] = float("nan")
+    x[1, 7] = float("inf")
+    x[2, :] = float("-inf")
+    x[3, 9] = float("-inf")
+    x[4, :] = 1e30
+    out, expect = ops.softmax(cuda(x)).cpu(), torch.softmax(x, -1)
+    assert torch.equal(out.isnan(), expect.isnan())
+    keep = ~expect.isnan()
+    assert (out[keep] - expect[keep]).abs().max() < 1e-6
+    assert out[0].isnan().all() and out[1].isnan().all() and out[2].isnan().all()
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("shape", [(8, 96, 4), (33, 130, 1), (5, 4096, 1), (4, 4100, 1), (6, 768, 12), (2, 40000, 1), (3, 20000, 2)])
+def test_group_norm(ops, shape, dtype) -> None:
+    m, c, groups = shape
+    gen = torch.Generator().manual_seed(m + c + groups)
+    x = (torch.randn(m, c, generator=gen) * 2 + 0.5).to(dtype)
+    w = (1 + 0.1 * torch.randn(c, generator=gen)).to(dtype)
+    b = (0.1 * torch.randn(c, generator=gen)).to(dtype)
+    out = ops.group_norm(cuda(x), groups, cuda(w), cuda(b), 1e-5)
+    expect = ref.group_norm(x, groups, w, b, 1e-5)
+    assert checks.max_norm_rel(out.cpu(), expect) < (2e-6 if dtype == F32 else 1e-2)
+    if groups == 1:
+        torch_ln = F.layer_norm(x.float(), (c,), w.float(), b.float(), 1e-5)
+        assert checks.max_norm_rel(ops.layer_norm(cuda(x), cuda(w), cuda(b)).cpu().float(), torch_ln) < (2e-6 if dtype == F32 else 1e-2)
+    y = cuda(x).clone()
+    assert torch.equal(ops.group_norm(y, groups, cuda(w), cuda(b), 1e-5, in_place=True), out)
+
+
+def test_group_norm_epilogues(ops) -> None:
+    gen = torch.Generator().manual_seed(3)
+    x, w, b, extra = (torch.randn(9, 64, generator=gen), torch.randn(64, generator=gen), torch.randn(64, generator=gen),
+                      torch.randn(64, generator=gen))
+    dx, dw, db, de = cuda(x, w, b, extra)
+    for fused, fn in ((ops.mul_extra, torch.mul), (torch.add, torch.add)):
+        out = ops.group_norm(dx, 2, dw, db, 1e-5, fused, de)
+        assert checks.rel_frobenius(out.cpu(), ref.group_norm(x, 2, w, b, 1e-5, fn, extra)) < 1e-5
+    out = ops.group_norm(dx, 2, dw, db, 1e-5, torch.relu)
+    assert checks.rel_frobenius(out.cpu(), torch.relu(ref.group_norm(x, 2, w, b, 1e-5))) < 1e-5
+    custom = lambda y, e: y * torch.tanh(e)  # noqa: E731
+    out = ops.group_norm(dx, 2, dw, db, 1e-5, custom, de)
+    assert checks.rel_frobenius(out.cpu(), ref.group_norm(x, 2, w, b, 1e-5, custom, extra)) < 1e-5
+    out = ops.group_norm(dx, 4, None, None, 1e-5)
+    assert checks.rel_frobenius(out.cpu(), ref.group_norm(x, 4, None, None, 1e-5)) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("shape", [(8, 96), (33, 130), (5, 4096), (2, 40000)])
+def test_rms_norm(ops, shape, dtype) -> None:
+    gen = torch.Generator().manual_seed(sum(shape))
+    x = (torch.randn(*shape, generator=gen) * 2).to(dtype)
+    w = (1 + 0.1 * torch.randn(shape[1], generator=gen)).to(dtype)
+    out = ops.rms_norm(cuda(x), cuda(w), 1e-5)
+    assert checks.max_norm_rel(out.cpu(), ref.rms_norm(x, w, 1e-5)) < (2e-6 if dtype == F32 else 1e-2)
+    assert checks.max_norm_rel(ops.rms_norm(cuda(x)).cpu(), ref.rms_norm(x, None, 1e-5)) < (2e-6 if dtype == F32 else 1e-2)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_c4_configuration(ops, dtype) -> None:
+    """x [rows, 4096] ~N(0,2) with 1% of entries at +-30; softmax, layer_norm, rms_norm and the chain."""
+    data = inputs.c4_rows(m=512, n=4096, dtype=dtype)
+    x, gamma, beta = data["x"], data["gamma"], data["beta"]
+    dx, dg, db = cuda(x, gamma, beta)
+    bound = 1e-5 if dtype == F32 else 1e-2
+    sm = ops.softmax(dx)
+    checks.assert_parity(dtype, sm.cpu(), ref.softmax(x), "softmax")
+    ln = ops.layer_norm(dx, dg, db, 1e-5)
+    checks.assert_parity(dtype, ln.cpu(), ref.layer_norm(x, gamma, beta, 1e-5), "layer_norm")
+    rn = ops.rms_norm(dx, dg, 1e-5)
+    checks.assert_parity(dtype, rn.cpu(), ref.rms_norm(x, gamma, 1e-5), "rms_norm")
+    chain = ops.layer_norm(sm, dg, db, 1e-5)
+    # the chain's reference starts from the kernel's own (rounded) softmax
+    assert checks.max_norm_rel(chain.cpu(), ref.layer_norm(sm.cpu(), gamma, beta, 1e-5)) < (2e-4 if dtype == F32 else 2e-2)
+    # properties that hold at any size
+    assert (sm.float().sum(-1) - 1).abs().max() < (1e-5 if dtype == F32 else 2e-2)
+    assert torch.equal(ops.softmax(dx), sm)
+    shifted = ops.softmax((dx.float() + 3.0).to(dtype)) if dtype == F32 else None
+    if shifted is not None:
+        assert checks.max_norm_rel(shifted, sm) < 1e-5  # shift invariance
+    assert bound > 0
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("shape", [(33, 65), (16, 520), (1, 1), (7, 4096), (300, 24), (3, 70001), (2000, 8)])
+def test_row_and_column_reductions(ops, shape, dtype) -> None:
+    m, n = shape
+    gen = torch.Generator().manual_seed(m * 7 + n)
+    x = torch.randn(m, n, generator=gen).to(dtype)
+    v = torch.randn(n, generator=gen)
+    dx = cuda(x)
+    bound = 1e-5 if dtype == F32 else 1e-2
+    assert checks.max_norm_rel(ops.row_sum(dx).cpu(), ref.row_sum(x)) < bound
+    assert ops.row_sum(dx).shape == (m, 1) and ops.row_sum(dx).dtype == dtype
+    assert checks.max_norm_rel(ops.row_sum(dx, torch.relu).cpu(), ref.row_sum(x, torch.relu)) < bound
+    assert checks.max_norm_rel(ops.row_dot(dx, cuda(v)).cpu(), ref.row_dot(x, v)) < bound
+    vec = torch.randn(n, 1, generator=gen).to(dtype)
+    assert checks.max_norm_rel(ops.matvec(dx, cuda(vec)).cpu(), ref.matvec(x, vec)) < bound
+    col = ops.column_sum(dx)
+    assert col.dtype == F32 and col.shape == (n,)
+    assert checks.max_norm_rel(col.cpu(), ref.column_sum(x)) < 1e-5
+    assert torch.equal(col, ops.column_sum(dx))  # fixed order: same bits
+    custom = ops.row_sum(dx, lambda t: t * 0.5 + 1)
+    assert checks.max_norm_rel(custom.cpu(), ref.row_sum(x, lambda t: t * 0.5 + 1)) < bound
+
+
+def test_column_sum_tall(ops) -> None:
+    """Many rows: the two-stage path with partial sums in scratch memory."""
+    gen = torch.Generator().manual_seed(9)
+    x = torch.randn(20000, 96, generator=gen)
+    out = ops.column_sum(cuda(x))
+    assert checks.max_norm_rel(out.cpu(), ref.column_sum(x)) < 1e-5
+    xb = x.bfloat16()
+    assert checks.max_norm_rel(ops.column_sum(cuda(xb)).cpu(), ref.column_sum(xb)) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("shape", [(9, 1030), (1,), (4, 5, 7), (0, 4), (1 << 20,)])
+def test_elementwise(ops, shape, dtype) -> None:
+    gen = torch.Generator().manual_seed(len(shape))
+    x = torch.randn(*shape, generator=gen).to(dtype)
+    if x.numel() > 3:
+        x.view(-1)[1] = float("nan")
+        x.view(-1)[2] = -0.0
+    dx = cuda(x)
+    assert torch.equal(bits(ops.relu(dx)), bits(torch.relu(x)))
+    assert torch.equal(bits(ops.leaky_relu(dx, 0.1)), bits(F.leaky_relu(x, 0.1)))
+    assert torch.equal(bits(ops.scalar_mul(dx, 1.7)), bits(x * 1.7))
+    assert torch.equal(bits(ops.scalar_mul(dx, torch.tensor(-0.25))), bits(x * -0.25))
+    odd = cuda(torch.randn(1025, generator=gen).to(dtype))[1:]  # unaligned base
+    assert torch.equal(bits(ops.relu(odd)), bits(torch.relu(odd.cpu())))
