@@ -542,17 +542,19 @@ struct UmmaPlan {
 UmmaPlan umma_plan(const b200_gemm_desc& d, int sm_count, bool parallel_splits) {
   UmmaPlan plan;
   const bool b_kmajor = d.b_layout == B200_LAYOUT_COL;
+  // BLOCK_N: a multiple of 32 (the epilogue reads the accumulator 32 columns at a
+  // time; UMMA needs N % 16 == 0), of 64 when B is N-contiguous (64-column TMA chunks).
+  const int gran = b_kmajor ? 32 : 64;
   int bn = 256;
   if (d.tile_n > 0) bn = static_cast<int>(round_up(d.tile_n, 64));
   if (bn > 256) bn = 256;
-  // Narrow problems: no wider than N needs (MN-major B tiles come in 64-column chunks).
-  const int64_t n_cap = round_up(d.n, b_kmajor ? 16 : 64);
+  // Narrow problems: no wider than N needs.
+  const int64_t n_cap = round_up(d.n, gran);
   if (bn > n_cap) bn = static_cast<int>(n_cap);
   // Too few tiles for the SMs: narrower tiles until every SM has work or 64 columns.
   const int64_t psplit_factor = (parallel_splits && d.split_k > 1) ? d.split_k : 1;
   while (d.tile_n <= 0 && bn > 64 && ceil_div(d.m, kBlockM) * ceil_div(d.n, bn) * d.batch * psplit_factor < sm_count)
-    bn /= 2;
-  if (!b_kmajor) bn = static_cast<int>(round_up(bn, 64));
+    bn = static_cast<int>(round_up(bn / 2, gran));
   plan.block_n = bn;
   const int want_splits = d.split_k > 1 ? d.split_k : 1;
   plan.psplits = parallel_splits ? want_splits : 1;
