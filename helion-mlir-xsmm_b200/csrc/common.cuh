@@ -123,13 +123,45 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// exp2 and reciprocal on the special-function unit (one instruction each).
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float fast_rcp(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// erf by the rational/exponential form 7.1.26 of Abramowitz & Stegun:
+// |error| <= 1.5e-7 plus the special-function unit's 2^-22 relative error; about
+// a dozen instructions instead of erff's thirty-odd with a divergent branch.
+__device__ __forceinline__ float fast_erf(float x) {
+  const float z = fabsf(x);
+  const float t = fast_rcp(fmaf(0.3275911f, z, 1.f));
+  float poly = fmaf(1.061405429f, t, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  poly *= t;
+  const float e = fast_exp2(z * z * -1.4426950408889634f);
+  return copysignf(fmaf(-poly, e, 1.f), x);
+}
+
+__device__ __forceinline__ float warp_fmax(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
 // Activations of fused epilogues, all in f32.
 __device__ __forceinline__ float apply_act(int act, float x, float alpha) {
   switch (act) {
     case B200_ACT_RELU:
       return (x != x) ? x : fmaxf(x, 0.f);
     case B200_ACT_GELU_ERF:
-      return 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
+      return 0.5f * x * (1.f + fast_erf(x * 0.70710678118654752f));
     case B200_ACT_GELU_TANH: {
       const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
       return 0.5f * x * (1.f + tanhf(u));

@@ -1,13 +1,14 @@
 // bf16 tensor-core GEMM for sm_100a: tcgen05.mma with the accumulator in tensor
 // memory, operands staged in shared memory by TMA, fused epilogue.
 //
-// One persistent CTA per SM, 6 warps:
-//   warps 0-3  epilogue: tcgen05.ld the 128 x BLOCK_N f32 accumulator (warp w owns
-//              TMEM lanes 32w..32w+31 = tile rows), + bias, * scale, + shift,
-//              activation, one rounding, stores to C
-//   warp 4     TMA producer: cp.async.bulk.tensor loads of the A and B stage
+// One persistent CTA per SM, 10 warps:
+//   warps 0-7  epilogue: tcgen05.ld the 128 x BLOCK_N f32 accumulator (warp w owns
+//              TMEM lanes 32(w%4)..+31 = tile rows and column half w/4), + bias,
+//              * scale, + shift, activation, one rounding, stores to C. Two warps
+//              per scheduler: one warp alone cannot hide its own latencies.
+//   warp 8     TMA producer: cp.async.bulk.tensor loads of the A and B stage
 //              (no cluster multicast: every CTA fetches its own tiles; reuse comes from L2)
-//   warp 5     MMA issuer: owns the TMEM allocation; one lane issues
+//   warp 9     MMA issuer: owns the TMEM allocation; one lane issues
 //              tcgen05.mma.cta_group::1.kind::f16 (M=128, N=BLOCK_N, K=16) and
 //              commits stage-empty / accumulator-full mbarriers
 // The accumulator is double buffered (2 x 256 TMEM columns), so the epilogue of
@@ -35,8 +36,10 @@ namespace {
 constexpr int kBlockM = 128;
 constexpr int kStageK = 64;  // bf16 elements per stage = one 128-byte swizzle row
 constexpr int kUmmaK = 16;
-constexpr int kThreads = 192;
-constexpr int kEpilogueWarps = 4;
+constexpr int kEpilogueWarps = 8;  // warp w: TMEM lane quarter w % 4, column half w / 4
+constexpr int kProducerWarp = kEpilogueWarps;
+constexpr int kMmaWarp = kEpilogueWarps + 1;
+constexpr int kThreads = 32 * (kEpilogueWarps + 2);
 constexpr int kMaxStages = 8;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccStride = 256;  // TMEM columns between the two accumulators
@@ -265,11 +268,11 @@ __global__ void __launch_bounds__(kThreads, 1)
     bars->abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 4 && lane == 0) {
+  if (warp == kProducerWarp && lane == 0) {
     tma_prefetch_desc(&map_a);
     tma_prefetch_desc(&map_b);
   }
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(&bars->tmem_base), kTmemCols);
     tmem_relinquish();
   }
@@ -278,7 +281,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     // ------------------------------------------------------------------ TMA producer
     uint32_t it = 0;
     bool ok = true;
@@ -321,7 +324,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const bool drained = mbar_wait(smem_u32(&bars->full[stage]), round & 1u, &never, p.status, kErrDrainWait);
       if (!__all_sync(0xffffffffu, drained)) break;
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer
     uint32_t it = 0, phase = 0;
     bool ok = true;
@@ -359,10 +362,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     // ------------------------------------------------------------------ epilogue
     uint32_t phase = 0;
     bool ok = true;
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const int quarter = warp & 3, half = warp >> 2;
+    const int half_cols = p.block_n >> 1;  // BLOCK_N is a multiple of 64
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     for (int64_t work = blockIdx.x; work < total_work && ok; work += gridDim.x) {
       const Tile t = tile_of(p, work);
-      const int64_t row = static_cast<int64_t>(t.m0) + warp * 32 + lane;
+      const int64_t row = static_cast<int64_t>(t.m0) + quarter * 32 + lane;
       const bool row_ok = row < p.m;
       uint8_t* c_row = static_cast<uint8_t*>(p.c) +
                        (static_cast<int64_t>(t.ksplit) * p.psplit_stride + static_cast<int64_t>(t.batch) * p.stride_c +
@@ -375,7 +380,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (!ok) break;
         tc_fence_after();
         const bool last = s == p.splits - 1;
-        for (int c0 = 0; c0 < p.block_n; c0 += 32) {
+        for (int c0 = half * half_cols; c0 < (half + 1) * half_cols; c0 += 32) {
           uint32_t raw[32];
           tmem_ld_32x32(tmem_base + lane_base + acc * kAccStride + c0, raw);
           tmem_ld_wait();
@@ -456,7 +461,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   // ------------------------------------------------------------------ teardown
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
@@ -542,9 +547,9 @@ struct UmmaPlan {
 UmmaPlan umma_plan(const b200_gemm_desc& d, int sm_count, bool parallel_splits) {
   UmmaPlan plan;
   const bool b_kmajor = d.b_layout == B200_LAYOUT_COL;
-  // BLOCK_N: a multiple of 32 (the epilogue reads the accumulator 32 columns at a
-  // time; UMMA needs N % 16 == 0), of 64 when B is N-contiguous (64-column TMA chunks).
-  const int gran = b_kmajor ? 32 : 64;
+  // BLOCK_N: a multiple of 64 (each half of the columns is read by its epilogue warps
+  // 32 at a time; an N-contiguous B arrives in 64-column TMA chunks).
+  const int gran = 64;
   int bn = 256;
   if (d.tile_n > 0) bn = static_cast<int>(round_up(d.tile_n, 64));
   if (bn > 256) bn = 256;

@@ -34,7 +34,8 @@ struct RowParams {
   int32_t act;
   float alpha;
   float eps;
-  int32_t tpr;  // threads per row
+  int32_t tpr;        // threads per row
+  int32_t param_vec;  // weight/bias/extra are 16-byte aligned: vector loads
 };
 
 __device__ __forceinline__ float load_param(const void* p, int64_t i, int bf16) {
@@ -49,7 +50,7 @@ constexpr int kMaxWarpsPerRow = 32;
 template <bool IS_MAX>
 __device__ __forceinline__ float row_reduce(float v, float* scratch, int warps_per_row, int row_in_cta,
                                             int warp_in_row, int lane) {
-  v = IS_MAX ? warp_max(v) : warp_sum(v);
+  v = IS_MAX ? warp_fmax(v) : warp_sum(v);
   if (warps_per_row == 1) return v;
   if (lane == 0) scratch[row_in_cta * warps_per_row + warp_in_row] = v;
   __syncthreads();
@@ -57,18 +58,52 @@ __device__ __forceinline__ float row_reduce(float v, float* scratch, int warps_p
   float r = scratch[row_in_cta * warps_per_row];
   for (int w = 1; w < warps_per_row; ++w) {
     const float o = scratch[row_in_cta * warps_per_row + w];
-    r = IS_MAX ? nan_max(r, o) : r + o;
+    r = IS_MAX ? fmaxf(r, o) : r + o;
   }
   return r;
 }
 
+// EPV parameters (weight / bias / extra) starting at element `i` as floats.
+// `vec`: the pointer is 16-byte aligned and `i` a multiple of EPV, so one or two
+// vector loads (cached: every row reads the same parameters) replace EPV scalar ones.
+template <int EPV>
+__device__ __forceinline__ void load_params(const void* p, int64_t i, int bf16, bool vec, float (&out)[EPV]) {
+  if (EPV > 1 && vec) {
+    if (bf16) {
+      if (EPV == 8) {
+        unpack16(ld_plain16(static_cast<const __nv_bfloat16*>(p) + i), reinterpret_cast<float(&)[8]>(out));
+      } else {  // 4 bf16 = 8 bytes
+        const uint2 q = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(p) + i);
+        out[0] = __uint_as_float(q.x << 16);
+        out[1] = __uint_as_float(q.x & 0xffff0000u);
+        out[2 % EPV] = __uint_as_float(q.y << 16);
+        out[3 % EPV] = __uint_as_float(q.y & 0xffff0000u);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < EPV; j += 4) {
+        const float4 q = *reinterpret_cast<const float4*>(static_cast<const float*>(p) + i + j);
+        out[j] = q.x;
+        out[(j + 1) % EPV] = q.y;
+        out[(j + 2) % EPV] = q.z;
+        out[(j + 3) % EPV] = q.w;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < EPV; ++j) out[j] = load_param(p, i + j, bf16);
+  }
+}
+
 // VPT values per thread held in registers. VEC: 16-byte accesses (rows 16-byte
-// aligned and n a multiple of the vector width), else element accesses.
-// MAXT: the largest CTA the instantiation is launched with (register budget).
-template <typename T, bool VEC, int VPT, int OP, int MAXT>
+// aligned and n a multiple of the vector width), else element accesses. FULL:
+// n == tpr * VPT, so no lane is masked. MAXT: the largest CTA the instantiation
+// is launched with (register budget).
+template <typename T, bool VEC, int VPT, int OP, int MAXT, bool FULL>
 __global__ void __launch_bounds__(MAXT) rowwise_kernel(const RowParams p) {
   constexpr int EPV = VEC ? Elem<T>::kVec : 1;
   constexpr int NV = VPT / EPV;
+  constexpr float kLog2e = 1.4426950408889634f;
   static_assert(NV >= 1, "values per thread below one vector");
   __shared__ float red_a[kMaxWarpsPerRow];
   __shared__ float red_b[kMaxWarpsPerRow];
@@ -82,50 +117,56 @@ __global__ void __launch_bounds__(MAXT) rowwise_kernel(const RowParams p) {
   const int warp_in_row = t >> 5;
   const T* __restrict__ x = reinterpret_cast<const T*>(p.x);
   T* __restrict__ y = reinterpret_cast<T*>(p.y);
-  const int64_t n = p.n;
+  const int n = static_cast<int>(p.n);
   const float inv_n = 1.f / static_cast<float>(n);
+  const int col0 = t * EPV;          // first column of this thread
+  const int col_step = tpr * EPV;    // columns between its vectors
+  const bool pvec = p.param_vec != 0;
 
   for (int64_t base = static_cast<int64_t>(blockIdx.x) * rows_per_cta; base < p.rows;
        base += static_cast<int64_t>(gridDim.x) * rows_per_cta) {
     const int64_t row = base + row_in_cta;
     const bool live = row < p.rows;
-    const T* xr = x + row * p.ld;
-    T* yr = y + row * p.ld;
+    const T* xr = x + row * p.ld + col0;
+    T* yr = y + row * p.ld + col0;
 
     float v[NV][EPV];
     bool have[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-      const int64_t col = (static_cast<int64_t>(i) * tpr + t) * EPV;
-      have[i] = live && col < n;
+      have[i] = live && (FULL || col0 + i * col_step < n);
       if constexpr (VEC) {
         if (have[i]) {
           float tmp[EPV];
-          unpack16(ld_stream16(xr + col), tmp);
+          unpack16(ld_stream16(xr + i * col_step), tmp);
 #pragma unroll
           for (int j = 0; j < EPV; ++j) v[i][j] = tmp[j];
         }
       } else {
-        if (have[i]) v[i][0] = Elem<T>::load(xr + col);
+        if (have[i]) v[i][0] = Elem<T>::load(xr + i * col_step);
       }
     }
 
     if (OP == kSoftmax) {
+      // NaN needs no special care in the maximum: a NaN element makes its own
+      // exponential NaN, hence the row sum and every output of the row, as torch gives.
       float top = -INFINITY;
 #pragma unroll
       for (int i = 0; i < NV; ++i)
         if (have[i]) {
 #pragma unroll
-          for (int j = 0; j < EPV; ++j) top = nan_max(top, v[i][j]);
+          for (int j = 0; j < EPV; ++j) top = fmaxf(top, v[i][j]);
         }
       top = row_reduce<true>(top, red_a, warps_per_row, row_in_cta, warp_in_row, lane);
+      // exp(x - top) = 2^((x - top) * log2e): the difference first, so that it is
+      // exact near the maximum whatever the magnitude of the row.
       float total = 0.f;
 #pragma unroll
       for (int i = 0; i < NV; ++i)
         if (have[i]) {
 #pragma unroll
           for (int j = 0; j < EPV; ++j) {
-            v[i][j] = exp2f((v[i][j] - top) * 1.4426950408889634f);
+            v[i][j] = fast_exp2((v[i][j] - top) * kLog2e);
             total += v[i][j];
           }
         }
@@ -152,25 +193,32 @@ __global__ void __launch_bounds__(MAXT) rowwise_kernel(const RowParams p) {
 #pragma unroll
           for (int j = 0; j < EPV; ++j) {
             v[i][j] -= mean;
-            q += v[i][j] * v[i][j];
+            q = fmaf(v[i][j], v[i][j], q);
           }
         }
       q = row_reduce<false>(q, red_b, warps_per_row, row_in_cta, warp_in_row, lane);
       const float rstd = rsqrtf(q * inv_n + p.eps);
-      const int64_t chan0 = (p.groups > 1 ? (row % p.groups) : 0) * n;
+      const int64_t chan0 = (p.groups > 1 ? (row % p.groups) : 0) * n + col0;
 #pragma unroll
       for (int i = 0; i < NV; ++i)
         if (have[i]) {
-          const int64_t col = (static_cast<int64_t>(i) * tpr + t) * EPV;
+          const int64_t c = chan0 + i * col_step;
+          float w[EPV], b[EPV], e[EPV];
+          if (p.weight) load_params<EPV>(p.weight, c, p.param_bf16, pvec, w);
+          if (p.bias) load_params<EPV>(p.bias, c, p.param_bf16, pvec, b);
+          if (p.extra_op != B200_NORM_EXTRA_NONE) load_params<EPV>(p.extra, c, p.param_bf16, pvec, e);
 #pragma unroll
           for (int j = 0; j < EPV; ++j) {
-            const int64_t c = chan0 + col + j;
             float r = v[i][j] * rstd;
-            if (p.weight) r *= load_param(p.weight, c, p.param_bf16);
-            if (p.bias) r += load_param(p.bias, c, p.param_bf16);
-            if (p.extra_op == B200_NORM_EXTRA_ADD) r += load_param(p.extra, c, p.param_bf16);
-            if (p.extra_op == B200_NORM_EXTRA_MUL) r *= load_param(p.extra, c, p.param_bf16);
-            v[i][j] = apply_act(p.act, r, p.alpha);
+            if (p.weight) r *= w[j];
+            if (p.bias) r += b[j];
+            if (p.extra_op == B200_NORM_EXTRA_ADD) r += e[j];
+            if (p.extra_op == B200_NORM_EXTRA_MUL) r *= e[j];
+            v[i][j] = r;
+          }
+          if (p.act != B200_ACT_IDENTITY) {
+#pragma unroll
+            for (int j = 0; j < EPV; ++j) v[i][j] = apply_act(p.act, v[i][j], p.alpha);
           }
         }
     } else {  // kRmsNorm
@@ -179,18 +227,19 @@ __global__ void __launch_bounds__(MAXT) rowwise_kernel(const RowParams p) {
       for (int i = 0; i < NV; ++i)
         if (have[i]) {
 #pragma unroll
-          for (int j = 0; j < EPV; ++j) q += v[i][j] * v[i][j];
+          for (int j = 0; j < EPV; ++j) q = fmaf(v[i][j], v[i][j], q);
         }
       q = row_reduce<false>(q, red_a, warps_per_row, row_in_cta, warp_in_row, lane);
       const float rstd = rsqrtf(q * inv_n + p.eps);
 #pragma unroll
       for (int i = 0; i < NV; ++i)
         if (have[i]) {
-          const int64_t col = (static_cast<int64_t>(i) * tpr + t) * EPV;
+          float w[EPV];
+          if (p.weight) load_params<EPV>(p.weight, col0 + i * col_step, p.param_bf16, pvec, w);
 #pragma unroll
           for (int j = 0; j < EPV; ++j) {
             float r = v[i][j] * rstd;
-            if (p.weight) r *= load_param(p.weight, col + j, p.param_bf16);
+            if (p.weight) r *= w[j];
             v[i][j] = r;
           }
         }
@@ -202,15 +251,160 @@ __global__ void __launch_bounds__(MAXT) rowwise_kernel(const RowParams p) {
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       if (!have[i]) continue;
-      const int64_t col = (static_cast<int64_t>(i) * tpr + t) * EPV;
       if constexpr (VEC) {
         float tmp[EPV];
 #pragma unroll
         for (int j = 0; j < EPV; ++j) tmp[j] = v[i][j];
-        st_stream16(yr + col, pack16(tmp));
+        st_stream16(yr + i * col_step, pack16(tmp));
       } else {
-        Elem<T>::store(yr + col, v[i][0]);
+        Elem<T>::store(yr + i * col_step, v[i][0]);
       }
+    }
+  }
+}
+
+// The common case without any masking or run-time feature tests: whole vectors
+// (n == tpr * VPT), 16-byte aligned rows and parameters, weight (and bias) present,
+// no extra operand, no activation. PT is the parameters' element type.
+template <int EPV, typename PT>
+__device__ __forceinline__ void load_param_vec(const PT* p, float (&out)[EPV]) {
+  constexpr int PER = 16 / sizeof(PT);  // parameters per 16-byte load
+  if constexpr (EPV == PER) {
+    unpack16(ld_plain16(p), out);
+  } else if constexpr (EPV == 2 * PER) {  // 8 bf16 values with f32 parameters: two loads
+    const uint4 lo = ld_plain16(p), hi = ld_plain16(p + PER);
+    out[0] = __uint_as_float(lo.x);
+    out[1] = __uint_as_float(lo.y);
+    out[2] = __uint_as_float(lo.z);
+    out[3] = __uint_as_float(lo.w);
+    out[4] = __uint_as_float(hi.x);
+    out[5] = __uint_as_float(hi.y);
+    out[6] = __uint_as_float(hi.z);
+    out[7] = __uint_as_float(hi.w);
+  } else {  // 4 f32 values with bf16 parameters: 8 bytes
+    const uint2 q = *reinterpret_cast<const uint2*>(p);
+    out[0] = __uint_as_float(q.x << 16);
+    out[1] = __uint_as_float(q.x & 0xffff0000u);
+    out[2] = __uint_as_float(q.y << 16);
+    out[3] = __uint_as_float(q.y & 0xffff0000u);
+  }
+}
+
+template <typename T, typename PT, int VPT, int OP, int MAXT>
+__global__ void __launch_bounds__(MAXT) rowwise_lean_kernel(const RowParams p) {
+  constexpr int EPV = Elem<T>::kVec;
+  constexpr int NV = VPT / EPV;
+  constexpr float kLog2e = 1.4426950408889634f;
+  __shared__ float red_a[kMaxWarpsPerRow];
+  __shared__ float red_b[kMaxWarpsPerRow];
+  const int tpr = p.tpr;
+  const int rows_per_cta = blockDim.x / tpr;
+  const int row_in_cta = threadIdx.x / tpr;
+  const int t = threadIdx.x - row_in_cta * tpr;
+  const int lane = threadIdx.x & 31;
+  const int warps_per_row = tpr >> 5;
+  const int warp_in_row = t >> 5;
+  const int col0 = t * EPV, col_step = tpr * EPV;
+  const T* __restrict__ x = reinterpret_cast<const T*>(p.x) + col0;
+  T* __restrict__ y = reinterpret_cast<T*>(p.y) + col0;
+  const PT* __restrict__ weight = reinterpret_cast<const PT*>(p.weight) + col0;
+  const PT* __restrict__ bias = reinterpret_cast<const PT*>(p.bias) + col0;
+  const float inv_n = 1.f / static_cast<float>(p.n);
+
+  // The next row's loads are issued before this row's reductions, so that a CTA
+  // always has a row in flight (twice the bytes in flight for NV more registers).
+  const int64_t row_stride = static_cast<int64_t>(gridDim.x) * rows_per_cta;
+  const int64_t first = static_cast<int64_t>(blockIdx.x) * rows_per_cta;
+  uint4 raw[NV];
+  {
+    const int64_t r0 = first + row_in_cta;
+    const T* xr = x + (r0 < p.rows ? r0 : p.rows - 1) * p.ld;  // dead rows re-read a valid row, store nothing
+#pragma unroll
+    for (int i = 0; i < NV; ++i) raw[i] = ld_stream16(xr + i * col_step);
+  }
+  for (int64_t base = first; base < p.rows; base += row_stride) {
+    const int64_t row = base + row_in_cta;
+    const bool live = row < p.rows;
+    const int64_t row_c = live ? row : p.rows - 1;
+    float v[NV][EPV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) unpack16(raw[i], v[i]);
+    if (base + row_stride < p.rows) {
+      const int64_t rn = row + row_stride;
+      const T* xn = x + (rn < p.rows ? rn : p.rows - 1) * p.ld;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) raw[i] = ld_stream16(xn + i * col_step);
+    }
+
+    if (OP == kSoftmax) {
+      float top = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int j = 0; j < EPV; ++j) top = fmaxf(top, v[i][j]);
+      top = row_reduce<true>(top, red_a, warps_per_row, row_in_cta, warp_in_row, lane);
+      float total = 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int j = 0; j < EPV; ++j) {
+          v[i][j] = fast_exp2((v[i][j] - top) * kLog2e);
+          total += v[i][j];
+        }
+      total = row_reduce<false>(total, red_b, warps_per_row, row_in_cta, warp_in_row, lane);
+      const float inv = 1.f / total;
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int j = 0; j < EPV; ++j) v[i][j] *= inv;
+    } else if (OP == kGroupNorm) {
+      float s = 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int j = 0; j < EPV; ++j) s += v[i][j];
+      s = row_reduce<false>(s, red_a, warps_per_row, row_in_cta, warp_in_row, lane);
+      const float mean = s * inv_n;
+      float q = 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int j = 0; j < EPV; ++j) {
+          v[i][j] -= mean;
+          q = fmaf(v[i][j], v[i][j], q);
+        }
+      q = row_reduce<false>(q, red_b, warps_per_row, row_in_cta, warp_in_row, lane);
+      const float rstd = rsqrtf(q * inv_n + p.eps);
+      const int chan0 = p.groups > 1 ? static_cast<int>(row_c % p.groups) * static_cast<int>(p.n) : 0;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        float w[EPV], b[EPV];
+        load_param_vec<EPV, PT>(weight + chan0 + i * col_step, w);
+        load_param_vec<EPV, PT>(bias + chan0 + i * col_step, b);
+#pragma unroll
+        for (int j = 0; j < EPV; ++j) v[i][j] = fmaf(v[i][j] * rstd, w[j], b[j]);
+      }
+    } else {
+      float q = 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int j = 0; j < EPV; ++j) q = fmaf(v[i][j], v[i][j], q);
+      q = row_reduce<false>(q, red_a, warps_per_row, row_in_cta, warp_in_row, lane);
+      const float rstd = rsqrtf(q * inv_n + p.eps);
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        float w[EPV];
+        load_param_vec<EPV, PT>(weight + i * col_step, w);
+#pragma unroll
+        for (int j = 0; j < EPV; ++j) v[i][j] = v[i][j] * rstd * w[j];
+      }
+      if (warps_per_row > 1) __syncthreads();  // same two-barrier cadence as the other ops
+    }
+    if (live) {
+      T* yr = y + row * p.ld;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) st_stream16(yr + i * col_step, pack16(v[i]));
     }
   }
 }
@@ -231,7 +425,7 @@ __global__ void __launch_bounds__(1024) rowwise_long_kernel(const RowParams p) {
     T* yr = y + row * p.ld;
     if (OP == kSoftmax) {
       float top = -INFINITY;
-      for (int64_t c = threadIdx.x; c < n; c += blockDim.x) top = nan_max(top, Elem<T>::load(xr + c));
+      for (int64_t c = threadIdx.x; c < n; c += blockDim.x) top = fmaxf(top, Elem<T>::load(xr + c));
       top = row_reduce<true>(top, red_a, warps, 0, warp, lane);
       float total = 0.f;
       for (int64_t c = threadIdx.x; c < n; c += blockDim.x)
@@ -281,11 +475,11 @@ __global__ void __launch_bounds__(1024) rowwise_long_kernel(const RowParams p) {
   }
 }
 
-template <typename T, bool VEC, int VPT, int OP, int MAXT>
-int launch_rowwise(const RowParams& p, int cta_threads, cudaStream_t stream) {
+template <typename T, bool VEC, int VPT, int OP, int MAXT, bool FULL>
+int launch_rowwise_full(const RowParams& p, int cta_threads, cudaStream_t stream) {
   const int rows_per_cta = cta_threads / p.tpr;
   int per_sm = 0;
-  auto kernel = rowwise_kernel<T, VEC, VPT, OP, MAXT>;
+  auto kernel = rowwise_kernel<T, VEC, VPT, OP, MAXT, FULL>;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, cta_threads, 0) != cudaSuccess || per_sm < 1)
     per_sm = 1;
   const int64_t wanted = ceil_div(p.rows, rows_per_cta);
@@ -293,6 +487,39 @@ int launch_rowwise(const RowParams& p, int cta_threads, cudaStream_t stream) {
   const unsigned grid = static_cast<unsigned>(wanted < resident ? wanted : resident);
   kernel<<<grid, cta_threads, 0, stream>>>(p);
   return launched();
+}
+
+template <typename T, typename PT, int VPT, int OP, int MAXT>
+int launch_rowwise_lean(const RowParams& p, int cta_threads, cudaStream_t stream) {
+  const int rows_per_cta = cta_threads / p.tpr;
+  int per_sm = 0;
+  auto kernel = rowwise_lean_kernel<T, PT, VPT, OP, MAXT>;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, cta_threads, 0) != cudaSuccess || per_sm < 1)
+    per_sm = 1;
+  const int64_t wanted = ceil_div(p.rows, rows_per_cta);
+  const int64_t resident = static_cast<int64_t>(device_info().sm_count) * per_sm;
+  kernel<<<static_cast<unsigned>(wanted < resident ? wanted : resident), cta_threads, 0, stream>>>(p);
+  return launched();
+}
+
+// Whether the lean kernel applies: no masks, vector parameters, plain affine form.
+inline bool lean_case(const RowParams& p, int op, int vpt, int epv) {
+  if (p.n != static_cast<int64_t>(p.tpr) * vpt || vpt % epv) return false;
+  if (op == kSoftmax) return true;
+  if (!p.param_vec || p.extra_op != B200_NORM_EXTRA_NONE || p.act != B200_ACT_IDENTITY || !p.weight) return false;
+  if (op == kGroupNorm) return p.bias != nullptr && p.groups * p.n < (int64_t(1) << 30);
+  return true;
+}
+
+template <typename T, bool VEC, int VPT, int OP, int MAXT>
+int launch_rowwise(const RowParams& p, int cta_threads, cudaStream_t stream) {
+  if constexpr (VEC) {
+    if (lean_case(p, OP, VPT, Elem<T>::kVec)) {
+      if (p.param_bf16) return launch_rowwise_lean<T, __nv_bfloat16, VPT, OP, MAXT>(p, cta_threads, stream);
+      return launch_rowwise_lean<T, float, VPT, OP, MAXT>(p, cta_threads, stream);
+    }
+  }
+  return launch_rowwise_full<T, VEC, VPT, OP, MAXT, false>(p, cta_threads, stream);
 }
 
 template <typename T, bool VEC, int OP>
@@ -335,6 +562,7 @@ int run_rowwise(RowParams p, cudaStream_t stream) {
   }
   const int vpt = vpt_needed <= 8 ? 8 : (vpt_needed <= 16 ? 16 : 32);
   p.tpr = tpr;
+  p.param_vec = vec && aligned(p.weight, 16) && aligned(p.bias, 16) && aligned(p.extra, 16);
   const int cta_threads = tpr > 256 ? tpr : 256;
   if (vec) return dispatch_vpt<T, true, OP>(p, vpt, cta_threads, stream);
   return dispatch_vpt<T, false, OP>(p, vpt, cta_threads, stream);
