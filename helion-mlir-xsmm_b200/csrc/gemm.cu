@@ -39,7 +39,7 @@ int validate(const b200_gemm_desc* d, Resolved* r) {
   if (d->a_layout < 0 || d->a_layout > B200_LAYOUT_BLOCKED) return B200_E_ARG;
   if (d->b_layout < 0 || d->b_layout > B200_LAYOUT_VNNI_PANELS) return B200_E_ARG;
   if (d->epilogue < 0 || d->epilogue >= B200_ACT_COUNT_) return B200_E_ARG;
-  if (d->force_kernel < 0 || d->force_kernel > 2) return B200_E_ARG;
+  if (d->force_kernel < 0 || d->force_kernel > 4) return B200_E_ARG;
   if (d->m < 0 || d->n < 0 || d->k < 0 || d->batch < 1) return B200_E_SHAPE;
   if (d->split_k < 0 || d->split_k > 1024) return B200_E_ARG;
   if ((d->b_layout == B200_LAYOUT_BLOCKED_VNNI || d->b_layout == B200_LAYOUT_VNNI_PANELS) && d->dtype != B200_BF16)
@@ -163,7 +163,7 @@ extern "C" int b200_gemm(const b200_gemm_desc* desc, void* stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int why = 0;
   const Path path = choose(d, r, &why);
-  if (path == kPathSimt && d.force_kernel == 1) return refuse(why ? why : B200_E_ARG);
+  if (path == kPathSimt && d.force_kernel != 0 && d.force_kernel != 2) return refuse(why ? why : B200_E_ARG);
 
   // Workspace carve-up: [unpacked B][split-K partials].
   uint8_t* ws = static_cast<uint8_t*>(d.workspace);
@@ -205,7 +205,7 @@ extern "C" int b200_gemm_explain(const b200_gemm_desc* desc, char* buf, size_t b
   if (path == kPathSimt) {
     snprintf(buf, buf_len, "simt_ffma tile=128x128x16 (tensor-core path not taken: %s)",
              desc->force_kernel == 2 ? "forced" : b200_strerror(why));
-    return desc->force_kernel == 1 ? (why ? why : B200_E_ARG) : 0;
+    return (desc->force_kernel != 0 && desc->force_kernel != 2) ? (why ? why : B200_E_ARG) : 0;
   }
   const b200_gemm_desc u = path == kPathUmmaUnpack ? unpacked_desc(*desc, r, desc->workspace) : *desc;
   char inner[200];

@@ -136,32 +136,91 @@ __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
 
+// CG is the tcgen05 cta_group: 1 (one CTA per tile) or 2 (a CTA pair on one TPC shares a tile).
+template <int CG>
 __device__ __forceinline__ void tmem_alloc(uint32_t result_smem, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(result_smem), "r"(cols)
-               : "memory");
+  if (CG == 1)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(result_smem), "r"(cols)
+                 : "memory");
+  else
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(result_smem), "r"(cols)
+                 : "memory");
 }
+template <int CG>
 __device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  if (CG == 1)
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  else
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
 }
+template <int CG>
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+  if (CG == 1)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+  else
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// In the shared::cluster window a CTA's own shared addresses carry its rank in
+// bit 24: clearing it names the same offset in the even (leader) CTA of a pair.
+constexpr uint32_t kLeaderMask = 0xFEFFFFFFu;
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on a barrier of the pair's leader CTA (which may be this CTA).
+__device__ __forceinline__ void mbar_arrive_leader(uint32_t bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar & kLeaderMask) : "memory");
+}
+// TMA load of a CTA pair: the bytes are counted on the leader's barrier.
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int32_t x,
+                                                 int32_t y, int32_t z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar & kLeaderMask), "r"(x), "r"(y), "r"(z)
+      : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+template <int CG>
 __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                           uint32_t accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
-      "}" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
+  if (CG == 1)
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  else
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
 }
-// Arrives on `bar` once every tcgen05.mma issued so far by this thread has completed.
+// Arrives on `bar` once every tcgen05.mma issued so far by this thread has
+// completed; for a CTA pair, on the barrier at that offset in both CTAs.
+template <int CG>
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+  if (CG == 1) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+  } else {
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::
+                     "r"(bar),
+                 "h"(both)
+                 : "memory");
+  }
 }
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -196,14 +255,14 @@ struct __align__(8) PipelineBarriers {
 struct Tile {
   int32_t batch, m0, n0, ksplit;
 };
-__device__ __forceinline__ Tile tile_of(const UmmaParams& p, int64_t work) {
+__device__ __forceinline__ Tile tile_of(const UmmaParams& p, int64_t work, int rows_per_tile, int row_offset) {
   Tile t;
   t.ksplit = static_cast<int32_t>(work % p.psplits);
   work /= p.psplits;
   const int64_t per_batch = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
   t.batch = static_cast<int32_t>(work / per_batch);
   const int64_t r = work - t.batch * per_batch;
-  t.m0 = static_cast<int32_t>(r / p.tiles_n) * kBlockM;
+  t.m0 = static_cast<int32_t>(r / p.tiles_n) * rows_per_tile + row_offset;
   t.n0 = static_cast<int32_t>(r % p.tiles_n) * p.block_n;
   return t;
 }
@@ -242,6 +301,7 @@ __device__ __forceinline__ void activate32(int act, float alpha, float (&v)[32])
   }
 }
 
+template <int CG>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_umma_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                           const UmmaParams p) {
@@ -255,6 +315,13 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t total_work = static_cast<int64_t>(p.batch) * p.tiles_m * p.tiles_n * p.psplits;
+  // A CTA pair (CG == 2) shares one 256-row tile: CTA `rank` owns rows 128*rank.. of it
+  // and stages half of the B tile; the even CTA (leader) issues the MMAs for both.
+  const int rank = CG == 2 ? static_cast<int>(cluster_cta_rank()) : 0;
+  const bool leader = rank == 0;
+  const int64_t first_work = blockIdx.x / CG, work_stride = gridDim.x / CG;
+  constexpr int kTileRows = kBlockM * CG;
+  const int b_rows = p.block_n / CG;  // columns of the B tile this CTA stages
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
@@ -263,7 +330,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&bars->acc_full[a]), 1);
-      mbar_init(smem_u32(&bars->acc_empty[a]), kEpilogueWarps);
+      mbar_init(smem_u32(&bars->acc_empty[a]), kEpilogueWarps * CG);
     }
     bars->abort_flag = 0;
     fence_barrier_init();
@@ -273,11 +340,14 @@ __global__ void __launch_bounds__(kThreads, 1)
     tma_prefetch_desc(&map_b);
   }
   if (warp == kMmaWarp) {
-    tmem_alloc(smem_u32(&bars->tmem_base), kTmemCols);
-    tmem_relinquish();
+    tmem_alloc<CG>(smem_u32(&bars->tmem_base), kTmemCols);
+    tmem_relinquish<CG>();
   }
   tc_fence_before();
-  __syncthreads();
+  if (CG == 2)
+    cluster_sync_all();  // the peer's barriers are initialised before anything is signalled on them
+  else
+    __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
 
@@ -285,8 +355,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     // ------------------------------------------------------------------ TMA producer
     uint32_t it = 0;
     bool ok = true;
-    for (int64_t work = blockIdx.x; work < total_work && ok; work += gridDim.x) {
-      const Tile t = tile_of(p, work);
+    for (int64_t work = first_work; work < total_work && ok; work += work_stride) {
+      const Tile t = tile_of(p, work, kTileRows, rank * kBlockM);
       for (int s = 0; s < p.splits && ok; ++s) {
         for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
           const uint32_t stage = it % p.stages, round = it / p.stages;
@@ -298,18 +368,24 @@ __global__ void __launch_bounds__(kThreads, 1)
             const uint32_t a_dst = smem_base + stage * stage_bytes;
             const uint32_t b_dst = a_dst + p.a_stage_bytes;
             const int32_t k0 = ((t.ksplit * p.splits + s) * p.k_blocks + kb) * kStageK;
-            mbar_expect_tx(full, stage_bytes);
+            const int32_t nb = t.n0 + rank * b_rows;  // this CTA's share of the B tile
+            // The leader's barrier counts the bytes of both CTAs of a pair.
+            if (leader) mbar_expect_tx(full, stage_bytes * CG);
+            auto load = [&](uint32_t dst, const CUtensorMap* map, int32_t c0, int32_t c1) {
+              if (CG == 2)
+                tma_load_3d_pair(dst, map, full, c0, c1, t.batch);
+              else
+                tma_load_3d(dst, map, full, c0, c1, t.batch);
+            };
             if (p.a_kmajor) {
-              tma_load_3d(a_dst, &map_a, full, k0, t.m0, t.batch);
+              load(a_dst, &map_a, k0, t.m0);
             } else {
-              for (int j = 0; j < kBlockM / 64; ++j)
-                tma_load_3d(a_dst + j * 8192, &map_a, full, t.m0 + 64 * j, k0, t.batch);
+              for (int j = 0; j < kBlockM / 64; ++j) load(a_dst + j * 8192, &map_a, t.m0 + 64 * j, k0);
             }
             if (p.b_kmajor) {
-              tma_load_3d(b_dst, &map_b, full, k0, t.n0, t.batch);
+              load(b_dst, &map_b, k0, nb);
             } else {
-              for (int j = 0; j < p.block_n / 64; ++j)
-                tma_load_3d(b_dst + j * 8192, &map_b, full, t.n0 + 64 * j, k0, t.batch);
+              for (int j = 0; j < b_rows / 64; ++j) load(b_dst + j * 8192, &map_b, nb + 64 * j, k0);
             }
           }
           __syncwarp();
@@ -317,18 +393,20 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
     // Drain: no stage this CTA armed may still be in flight when its shared memory is given up.
+    // (A pair's peer has no barrier of its own to ask: its last loads have landed once the
+    // leader's MMAs that read them completed, which its epilogue waits for.)
     const uint32_t first = it > static_cast<uint32_t>(p.stages) ? it - p.stages : 0;
-    for (uint32_t j = first; j < it; ++j) {
+    for (uint32_t j = leader ? first : it; j < it; ++j) {
       const uint32_t stage = j % p.stages, round = j / p.stages;
       int never = 0;
       const bool drained = mbar_wait(smem_u32(&bars->full[stage]), round & 1u, &never, p.status, kErrDrainWait);
       if (!__all_sync(0xffffffffu, drained)) break;
     }
   } else if (warp == kMmaWarp) {
-    // ------------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------------ MMA issuer (the leader's, for a pair)
     uint32_t it = 0, phase = 0;
-    bool ok = true;
-    for (int64_t work = blockIdx.x; work < total_work && ok; work += gridDim.x) {
+    bool ok = leader;
+    for (int64_t work = first_work; work < total_work && ok; work += work_stride) {
       for (int s = 0; s < p.splits && ok; ++s, ++phase) {
         const uint32_t acc = phase & 1u, acc_round = phase >> 1;
         ok = mbar_wait(smem_u32(&bars->acc_empty[acc]), (acc_round & 1u) ^ 1u, abort_flag, p.status, kErrMmaWait);
@@ -349,10 +427,10 @@ __global__ void __launch_bounds__(kThreads, 1)
             const uint64_t b_desc = make_desc(b_addr, p.b_desc_lbo, p.b_desc_hi);
 #pragma unroll
             for (int j = 0; j < kStageK / kUmmaK; ++j)
-              umma_bf16(d_tmem, a_desc + static_cast<uint64_t>(j * p.a_kstep),
-                        b_desc + static_cast<uint64_t>(j * p.b_kstep), p.idesc, (kb | j) != 0 ? 1u : 0u);
-            umma_commit(smem_u32(&bars->empty[stage]));
-            if (kb == p.k_blocks - 1) umma_commit(smem_u32(&bars->acc_full[acc]));
+              umma_bf16<CG>(d_tmem, a_desc + static_cast<uint64_t>(j * p.a_kstep),
+                            b_desc + static_cast<uint64_t>(j * p.b_kstep), p.idesc, (kb | j) != 0 ? 1u : 0u);
+            umma_commit<CG>(smem_u32(&bars->empty[stage]));
+            if (kb == p.k_blocks - 1) umma_commit<CG>(smem_u32(&bars->acc_full[acc]));
           }
           __syncwarp();
         }
@@ -365,8 +443,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int quarter = warp & 3, half = warp >> 2;
     const int half_cols = p.block_n >> 1;  // BLOCK_N is a multiple of 64
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-    for (int64_t work = blockIdx.x; work < total_work && ok; work += gridDim.x) {
-      const Tile t = tile_of(p, work);
+    for (int64_t work = first_work; work < total_work && ok; work += work_stride) {
+      const Tile t = tile_of(p, work, kTileRows, rank * kBlockM);
       const int64_t row = static_cast<int64_t>(t.m0) + quarter * 32 + lane;
       const bool row_ok = row < p.m;
       uint8_t* c_row = static_cast<uint8_t*>(p.c) +
@@ -453,17 +531,27 @@ __global__ void __launch_bounds__(kThreads, 1)
         // This warp has read the whole accumulator: hand it back to the MMA warp.
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty[acc]));
+        if (lane == 0) {
+          if (CG == 2)
+            mbar_arrive_leader(smem_u32(&bars->acc_empty[acc]));
+          else
+            mbar_arrive(smem_u32(&bars->acc_empty[acc]));
+        }
       }
     }
   }
 
   // ------------------------------------------------------------------ teardown
+  // Neither CTA of a pair may leave while the other can still read its shared
+  // memory (MMA operands) or signal its barriers.
   tc_fence_before();
-  __syncthreads();
+  if (CG == 2)
+    cluster_sync_all();
+  else
+    __syncthreads();
   if (warp == kMmaWarp) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    tmem_dealloc<CG>(tmem_base, kTmemCols);
   }
 }
 
@@ -502,7 +590,7 @@ bool encode_map(CUtensorMap* map, const void* base, int64_t cols, int64_t rows, 
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-uint32_t make_idesc(int block_n, bool a_kmajor, bool b_kmajor) {
+uint32_t make_idesc(int block_n, bool a_kmajor, bool b_kmajor, int cta_group) {
   uint32_t d = 0;
   d |= 1u << 4;   // D format f32
   d |= 1u << 7;   // A format bf16
@@ -510,7 +598,7 @@ uint32_t make_idesc(int block_n, bool a_kmajor, bool b_kmajor) {
   d |= (a_kmajor ? 0u : 1u) << 15;
   d |= (b_kmajor ? 0u : 1u) << 16;
   d |= static_cast<uint32_t>(block_n >> 3) << 17;
-  d |= static_cast<uint32_t>(kBlockM >> 4) << 24;
+  d |= static_cast<uint32_t>((kBlockM * cta_group) >> 4) << 24;  // a CTA pair multiplies 256 rows
   return d;
 }
 
@@ -535,6 +623,7 @@ int umma_supports(const b200_gemm_desc& d) {
 }
 
 struct UmmaPlan {
+  int cta_group;  // 1: one CTA per 128-row tile; 2: a CTA pair per 256-row tile
   int block_n;
   int stages;
   int splits;   // serial
@@ -566,13 +655,28 @@ UmmaPlan umma_plan(const b200_gemm_desc& d, int sm_count, bool parallel_splits) 
   plan.splits = parallel_splits ? 1 : want_splits;
   const int64_t k_blocks_total = ceil_div(d.k, kStageK);
   plan.k_blocks = static_cast<int>(ceil_div(k_blocks_total, want_splits));
-  const size_t stage = static_cast<size_t>(kBlockM) * 128 + static_cast<size_t>(bn) * 128;
+  // CTA pairs halve the B bytes each SM stages per FLOP (deeper pipeline, less L2
+  // traffic). Taken when both halves of the B tile are whole 64-column chunks and
+  // the pairs' waves do not outlast the single CTAs' (a pair's tile takes about
+  // 0.85 of the time of two single tiles).
+  const int64_t per_row_tile = ceil_div(d.n, bn) * d.batch * plan.psplits;
+  const int64_t work1 = ceil_div(d.m, kBlockM) * per_row_tile, work2 = ceil_div(d.m, 2 * kBlockM) * per_row_tile;
+  const int pairs = sm_count / 2;
+  const double waves1 = static_cast<double>(ceil_div(work1, sm_count));
+  const double waves2 = pairs > 0 ? static_cast<double>(ceil_div(work2, pairs)) : 1e30;
+  plan.cta_group = (bn % 128 == 0 && pairs > 0 && waves2 * 0.85 <= waves1) ? 2 : 1;
+  if (d.force_kernel == 3) plan.cta_group = 1;
+  if (d.force_kernel == 4 && bn % 128 == 0 && pairs > 0) plan.cta_group = 2;
+  const int cg = plan.cta_group;
+  const size_t stage = static_cast<size_t>(kBlockM) * 128 + static_cast<size_t>(bn / cg) * 128;
   int stages = static_cast<int>((size_t(227) * 1024 - 2048) / stage);
   if (stages > kMaxStages) stages = kMaxStages;
   plan.stages = stages;
   plan.smem = stage * stages + 1024 + sizeof(PipelineBarriers);
-  const int64_t work = ceil_div(d.m, kBlockM) * ceil_div(d.n, bn) * d.batch * plan.psplits;
-  plan.grid = static_cast<unsigned>(work < sm_count ? work : sm_count);
+  if (cg == 2)
+    plan.grid = 2 * static_cast<unsigned>(work2 < pairs ? work2 : pairs);
+  else
+    plan.grid = static_cast<unsigned>(work1 < sm_count ? work1 : sm_count);
   return plan;
 }
 
@@ -595,7 +699,7 @@ int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* parti
   if (!ok) return refuse(B200_E_DEVICE);
   if (b_kmajor)
     ok = encode_map(&map_b, d.b, d.k, d.n, d.batch, d.ldb, d.batch > 1 ? d.stride_b : d.ldb * d.n, kStageK,
-                    plan.block_n);
+                    plan.block_n / plan.cta_group);
   else
     ok = encode_map(&map_b, d.b, d.n, d.k, d.batch, d.ldb, d.batch > 1 ? d.stride_b : d.ldb * d.k, 64, kStageK);
   if (!ok) return refuse(B200_E_DEVICE);
@@ -605,7 +709,7 @@ int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* parti
   p.n = static_cast<int32_t>(d.n);
   p.k = static_cast<int32_t>(d.k);
   p.batch = static_cast<int32_t>(d.batch);
-  p.tiles_m = static_cast<int32_t>(ceil_div(d.m, kBlockM));
+  p.tiles_m = static_cast<int32_t>(ceil_div(d.m, kBlockM * plan.cta_group));
   p.tiles_n = static_cast<int32_t>(ceil_div(d.n, plan.block_n));
   p.splits = plan.splits;
   p.psplits = plan.psplits;
@@ -614,9 +718,9 @@ int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* parti
   p.stages = plan.stages;
   p.a_kmajor = a_kmajor;
   p.b_kmajor = b_kmajor;
-  p.idesc = make_idesc(plan.block_n, a_kmajor, b_kmajor);
+  p.idesc = make_idesc(plan.block_n, a_kmajor, b_kmajor, plan.cta_group);
   p.a_stage_bytes = kBlockM * 128;
-  p.b_stage_bytes = static_cast<uint32_t>(plan.block_n) * 128;
+  p.b_stage_bytes = static_cast<uint32_t>(plan.block_n / plan.cta_group) * 128;  // this CTA's share of the B tile
   // K-major: 8-row groups 1024 B apart, K step = 32 B inside the swizzled row.
   // MN-major: 8-k-row groups 1024 B apart (SBO), 64-column chunks 8 KiB apart (LBO), K step = 16 rows = 2 KiB.
   p.a_desc_hi = desc_hi(1024);
@@ -645,9 +749,30 @@ int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* parti
   p.status = kernel_status_word();
 
   std::call_once(g_attr_once[dev.device], [] {
-    cudaFuncSetAttribute(gemm_umma_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaFuncSetAttribute(gemm_umma_bf16_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaFuncSetAttribute(gemm_umma_bf16_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
   });
-  gemm_umma_bf16_kernel<<<plan.grid, kThreads, plan.smem, stream>>>(map_a, map_b, p);
+  if (plan.cta_group == 2) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(plan.grid);
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = plan.smem;
+    config.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    config.attrs = &attr;
+    config.numAttrs = 1;
+    const cudaError_t err = cudaLaunchKernelEx(&config, gemm_umma_bf16_kernel<2>, map_a, map_b, p);
+    if (err != cudaSuccess) {
+      cudaGetLastError();
+      return finish(-static_cast<int>(err));
+    }
+  } else {
+    gemm_umma_bf16_kernel<1><<<plan.grid, kThreads, plan.smem, stream>>>(map_a, map_b, p);
+  }
   if (!parallel) return launched();
   const int rc = check_launch();
   if (rc != 0) return finish(rc);
@@ -659,8 +784,9 @@ int explain_gemm_umma(const b200_gemm_desc& d, char* buf, size_t len) {
   const DeviceInfo& dev = device_info();
   const bool parallel = d.workspace != nullptr && d.split_k > 1;
   const UmmaPlan plan = umma_plan(d, dev.sm_count > 0 ? dev.sm_count : 148, parallel);
-  snprintf(buf, len, "umma_bf16 tile=%dx%dx%d stages=%d serial_splits=%d parallel_splits=%d grid=%u smem=%zu", kBlockM,
-           plan.block_n, kStageK, plan.stages, plan.splits, plan.psplits, plan.grid, plan.smem);
+  snprintf(buf, len, "umma_bf16 cta_group=%d tile=%dx%dx%d stages=%d serial_splits=%d parallel_splits=%d grid=%u smem=%zu",
+           plan.cta_group, kBlockM * plan.cta_group, plan.block_n, kStageK, plan.stages, plan.splits, plan.psplits,
+           plan.grid, plan.smem);
   return 0;
 }
 

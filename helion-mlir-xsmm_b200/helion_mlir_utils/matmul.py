@@ -307,11 +307,12 @@ class GemmPlan:
         return out
 
     def explain(self, a: Tensor, b: Tensor) -> CallExplanation:
-        desc = self.desc
+        desc = native.GemmDesc.from_buffer_copy(self.desc)  # the plan's own descriptor stays as planned
         desc.a, desc.b = a.data_ptr(), b.data_ptr()
         desc.c = 1 << 46  # only compared with the operands' address ranges, never dereferenced
         desc.bias = desc.scale = desc.shift = None
         desc.bias_n = desc.scale_n = desc.shift_n = 0
+        desc.workspace, desc.workspace_bytes = (1 << 45 if self._wants_workspace else None), (1 << 40 if self._wants_workspace else 0)
         buf = ctypes.create_string_buffer(256)
         code = native.module().b200_gemm_explain(ctypes.byref(desc), buf, len(buf))
         text = buf.value.decode()

@@ -114,7 +114,8 @@ typedef struct b200_gemm_desc {
   int32_t tile_m, tile_n, tile_k;        /* block_sizes hint (0: choose); snapped to what the kernels implement */
   void* workspace;
   size_t workspace_bytes;
-  int32_t force_kernel;  /* 0 auto, 1 tensor-core (tcgen05) path or refuse, 2 SIMT FFMA path */
+  int32_t force_kernel;  /* 0 auto, 1 tensor-core (tcgen05) path or refuse, 2 SIMT FFMA path,
+                            3 tensor-core path with one CTA per tile, 4 with a CTA pair per tile (where the tile allows) */
   int32_t reserved_;
 } b200_gemm_desc;
 

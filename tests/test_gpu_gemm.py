@@ -199,3 +199,33 @@ def test_c_abi_refuses_what_it_cannot_run(ops) -> None:
     desc.c = torch.zeros(64, 64, device="cuda", dtype=BF16).data_ptr()
     desc.ldc = 32
     assert lib.b200_gemm(ctypes.byref(desc), native.stream_ptr(a.device)) == 3
+
+
+@pytest.mark.parametrize("cta_group", [1, 2])
+@pytest.mark.parametrize("trans_a", [False, True])
+@pytest.mark.parametrize("trans_b", [False, True])
+@pytest.mark.parametrize("shape", [(256, 256, 64), (640, 384, 320), (304, 264, 136), (1024, 512, 1024)])
+def test_single_cta_and_cta_pair_tiles_agree(ops, shape, trans_a: bool, trans_b: bool, cta_group: int) -> None:
+    """Both tilings of the tcgen05 kernel (one CTA per 128-row tile, a CTA pair per
+    256-row tile) against the oracle, with a fused epilogue and ragged edges."""
+    import importlib
+
+    from helion_mlir_backend import native
+
+    mm = importlib.import_module("helion_mlir_utils.matmul")
+    m, n, k = shape
+    gen = torch.Generator().manual_seed(m + 3 * n + 5 * k + trans_a + 2 * trans_b)
+    a, b, bias = rand(gen, m, k), rand(gen, k, n, scale=0.25), rand(gen, n)
+    a_in = a.T.contiguous() if trans_a else a
+    b_in = b.T.contiguous() if trans_b else b
+    da, db, dbias = cuda(a_in, b_in, bias)
+    plan = mm._plan_gemm(
+        a=da, m=m, n=n, k=k, a_layout=native.LAYOUT_COL if trans_a else native.LAYOUT_ROW,
+        b_layout=native.LAYOUT_COL if trans_b else native.LAYOUT_ROW, lda=da.shape[1], ldb=db.shape[1],
+        bias=dbias, scale=None, shift=None, epilogue=torch.relu, force_kernel=2 + cta_group, tiles=(128, 128, 64),
+    )
+    text = str(plan.explain(da, db))
+    assert f"cta_group={cta_group}" in text, text
+    out = plan.run(da, db, dbias)
+    checks.assert_parity(BF16, out.cpu(), ref.matmul(a, b, bias=bias, epilogue=torch.relu), text)
+    assert torch.equal(out, plan.run(da, db, dbias))
