@@ -353,22 +353,23 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------------ TMA producer
-    uint32_t it = 0;
-    bool ok = true;
-    for (int64_t work = first_work; work < total_work && ok; work += work_stride) {
-      const Tile t = tile_of(p, work, kTileRows, rank * kBlockM);
-      for (int s = 0; s < p.splits && ok; ++s) {
-        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
-          const uint32_t stage = it % p.stages, round = it / p.stages;
-          ok = mbar_wait(smem_u32(&bars->empty[stage]), (round & 1u) ^ 1u, abort_flag, p.status, kErrProducerWait);
-          ok = __all_sync(0xffffffffu, ok) != 0;
-          if (!ok) break;
-          if (lane == 0) {
+    // One lane runs the whole loop (the other lanes wait at the __syncwarp below):
+    // no per-stage votes, and stage / parity advance by increments, not divisions.
+    if (lane == 0) {
+      uint32_t stage = 0, parity = 1;  // a fresh barrier's preceding phase counts as complete
+      uint32_t issued = 0;
+      bool ok = true;
+      for (int64_t work = first_work; work < total_work && ok; work += work_stride) {
+        const Tile t = tile_of(p, work, kTileRows, rank * kBlockM);
+        const int32_t nb = t.n0 + rank * b_rows;  // this CTA's share of the B tile
+        for (int s = 0; s < p.splits && ok; ++s) {
+          int32_t k0 = (t.ksplit * p.splits + s) * p.k_blocks * kStageK;
+          for (int kb = 0; kb < p.k_blocks; ++kb, k0 += kStageK) {
+            ok = mbar_wait(smem_u32(&bars->empty[stage]), parity, abort_flag, p.status, kErrProducerWait);
+            if (!ok) break;
             const uint32_t full = smem_u32(&bars->full[stage]);
             const uint32_t a_dst = smem_base + stage * stage_bytes;
             const uint32_t b_dst = a_dst + p.a_stage_bytes;
-            const int32_t k0 = ((t.ksplit * p.splits + s) * p.k_blocks + kb) * kStageK;
-            const int32_t nb = t.n0 + rank * b_rows;  // this CTA's share of the B tile
             // The leader's barrier counts the bytes of both CTAs of a pair.
             if (leader) mbar_expect_tx(full, stage_bytes * CG);
             auto load = [&](uint32_t dst, const CUtensorMap* map, int32_t c0, int32_t c1) {
@@ -387,55 +388,76 @@ __global__ void __launch_bounds__(kThreads, 1)
             } else {
               for (int j = 0; j < b_rows / 64; ++j) load(b_dst + j * 8192, &map_b, nb + 64 * j, k0);
             }
+            ++issued;
+            if (++stage == static_cast<uint32_t>(p.stages)) {
+              stage = 0;
+              parity ^= 1u;
+            }
           }
-          __syncwarp();
+        }
+      }
+      // Drain: no stage this CTA armed may still be in flight when its shared memory is
+      // given up. (A pair's peer has no barrier of its own to ask: its last loads have
+      // landed once the leader's MMAs that read them completed, which its epilogue waits for.)
+      if (leader) {
+        const uint32_t pending = issued < static_cast<uint32_t>(p.stages) ? issued : p.stages;
+        // walk back `pending` stages from the next one to be armed
+        uint32_t st = stage, par = parity ^ 1u;  // parity the consumer waits for in the current round
+        for (uint32_t j = 0; j < pending; ++j) {
+          if (st == 0) {
+            st = p.stages;
+            par ^= 1u;
+          }
+          --st;
+          int never = 0;
+          if (!mbar_wait(smem_u32(&bars->full[st]), par, &never, p.status, kErrDrainWait)) break;
         }
       }
     }
-    // Drain: no stage this CTA armed may still be in flight when its shared memory is given up.
-    // (A pair's peer has no barrier of its own to ask: its last loads have landed once the
-    // leader's MMAs that read them completed, which its epilogue waits for.)
-    const uint32_t first = it > static_cast<uint32_t>(p.stages) ? it - p.stages : 0;
-    for (uint32_t j = leader ? first : it; j < it; ++j) {
-      const uint32_t stage = j % p.stages, round = j / p.stages;
-      int never = 0;
-      const bool drained = mbar_wait(smem_u32(&bars->full[stage]), round & 1u, &never, p.status, kErrDrainWait);
-      if (!__all_sync(0xffffffffu, drained)) break;
-    }
+    __syncwarp();
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer (the leader's, for a pair)
-    uint32_t it = 0, phase = 0;
-    bool ok = leader;
-    for (int64_t work = first_work; work < total_work && ok; work += work_stride) {
-      for (int s = 0; s < p.splits && ok; ++s, ++phase) {
-        const uint32_t acc = phase & 1u, acc_round = phase >> 1;
-        ok = mbar_wait(smem_u32(&bars->acc_empty[acc]), (acc_round & 1u) ^ 1u, abort_flag, p.status, kErrMmaWait);
-        ok = __all_sync(0xffffffffu, ok) != 0;
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * kAccStride;
-        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
-          const uint32_t stage = it % p.stages, round = it / p.stages;
-          ok = mbar_wait(smem_u32(&bars->full[stage]), round & 1u, abort_flag, p.status, kErrMmaWait);
-          ok = __all_sync(0xffffffffu, ok) != 0;
+    // The tensor core takes a new MMA only as the previous ones drain, so every cycle
+    // this thread spends between two MMAs is a cycle the tensor core idles: one lane,
+    // no votes, no divisions, descriptors advanced by increments.
+    if (lane == 0 && leader) {
+      uint32_t stage = 0, parity = 0;
+      uint32_t phase = 0;
+      const uint32_t stage_step = stage_bytes >> 4;
+      bool ok = true;
+      for (int64_t work = first_work; work < total_work && ok; work += work_stride) {
+        for (int s = 0; s < p.splits && ok; ++s, ++phase) {
+          const uint32_t acc = phase & 1u, acc_round = phase >> 1;
+          ok = mbar_wait(smem_u32(&bars->acc_empty[acc]), (acc_round & 1u) ^ 1u, abort_flag, p.status, kErrMmaWait);
           if (!ok) break;
           tc_fence_after();
-          if (lane == 0) {
-            const uint32_t a_addr = smem_base + stage * stage_bytes;
-            const uint32_t b_addr = a_addr + p.a_stage_bytes;
-            const uint64_t a_desc = make_desc(a_addr, p.a_desc_lbo, p.a_desc_hi);
-            const uint64_t b_desc = make_desc(b_addr, p.b_desc_lbo, p.b_desc_hi);
+          const uint32_t d_tmem = tmem_base + acc * kAccStride;
+          uint32_t accumulate = 0;
+          for (int kb = 0; kb < p.k_blocks; ++kb) {
+            ok = mbar_wait(smem_u32(&bars->full[stage]), parity, abort_flag, p.status, kErrMmaWait);
+            if (!ok) break;
+            tc_fence_after();
+            const uint64_t a_desc =
+                make_desc(smem_base, p.a_desc_lbo, p.a_desc_hi) + static_cast<uint64_t>(stage * stage_step);
+            const uint64_t b_desc = make_desc(smem_base + p.a_stage_bytes, p.b_desc_lbo, p.b_desc_hi) +
+                                    static_cast<uint64_t>(stage * stage_step);
 #pragma unroll
-            for (int j = 0; j < kStageK / kUmmaK; ++j)
+            for (int j = 0; j < kStageK / kUmmaK; ++j) {
               umma_bf16<CG>(d_tmem, a_desc + static_cast<uint64_t>(j * p.a_kstep),
-                            b_desc + static_cast<uint64_t>(j * p.b_kstep), p.idesc, (kb | j) != 0 ? 1u : 0u);
+                            b_desc + static_cast<uint64_t>(j * p.b_kstep), p.idesc, accumulate);
+              accumulate = 1;
+            }
             umma_commit<CG>(smem_u32(&bars->empty[stage]));
-            if (kb == p.k_blocks - 1) umma_commit<CG>(smem_u32(&bars->acc_full[acc]));
+            if (++stage == static_cast<uint32_t>(p.stages)) {
+              stage = 0;
+              parity ^= 1u;
+            }
           }
-          __syncwarp();
+          if (ok) umma_commit<CG>(smem_u32(&bars->acc_full[acc]));
         }
       }
     }
+    __syncwarp();
   } else {
     // ------------------------------------------------------------------ epilogue
     uint32_t phase = 0;
