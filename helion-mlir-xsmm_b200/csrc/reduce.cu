@@ -5,6 +5,8 @@
 // in index order), so two runs give the same bits. They replace
 // _row_sum_kernel, _row_dot_kernel, _matvec_kernel and _column_sum_kernel of
 // helion_mlir_utils/reduction.py.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -230,6 +232,39 @@ size_t column_sum_workspace(int64_t m, int64_t n) {
   return chunks > 1 ? static_cast<size_t>(chunks) * n * sizeof(float) : 0;
 }
 
+// ---------------------------------------------------------------------------
+// Scratch for b200_column_sum_static: a fixed array in the library's own device
+// image instead of caller-provided or freshly allocated memory. Every GPU that
+// loads the library carries these bytes until the process exits.
+// ---------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = B200_COLUMN_SUM_STATIC_MAX_BYTES;
+static __device__ __align__(256) unsigned char g_column_scratch[kStaticScratchBytes];
+
+constexpr int kScratchDevices = 64;
+std::mutex g_scratch_mutex;
+void* g_scratch_address[kScratchDevices];  // device address of g_column_scratch, per device (0: not looked up yet)
+
+// The array's name is only a host-side handle here: the address kernels can use
+// has to be asked for, once per device and with that device current.
+int static_scratch(void** out) {
+  int device = -1;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return -static_cast<int>(err);
+  if (device < 0 || device >= kScratchDevices) return B200_E_DEVICE;
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (!g_scratch_address[device]) {
+    void* address = nullptr;
+    err = cudaGetSymbolAddress(&address, g_column_scratch);
+    if (err != cudaSuccess) {
+      cudaGetLastError();
+      return -static_cast<int>(err);
+    }
+    g_scratch_address[device] = address;
+  }
+  *out = g_scratch_address[device];
+  return 0;
+}
+
 }  // namespace
 }  // namespace b200
 
@@ -269,4 +304,25 @@ extern "C" int b200_column_sum(int32_t dtype, const void* x, float* out, int64_t
   if (ld < n) return refuse(B200_E_STRIDE);
   if (device_info().sm_count == 0) return refuse(B200_E_DEVICE);
   return column_sum_impl(dtype, x, out, m, n, ld, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+// Same result as b200_column_sum, for callers that must not allocate and have no
+// scratch of their own to lend: the partial sums go to the library's fixed array.
+extern "C" int b200_column_sum_static(int32_t dtype, const void* x, float* out, int64_t m, int64_t n, int64_t ld,
+                                      void* stream) {
+  if (!enabled()) return refuse(B200_E_DISABLED);
+  if (!valid_dtype(dtype)) return refuse(B200_E_DTYPE);
+  if (m < 1 || n < 0) return refuse(B200_E_SHAPE);
+  if (n == 0) return finish(0);
+  if (!x || !out) return refuse(B200_E_NULL);
+  if (ld < n) return refuse(B200_E_STRIDE);
+  if (device_info().sm_count == 0) return refuse(B200_E_DEVICE);
+  // The partial sums of this shape must fit the fixed array.
+  if (column_sum_workspace(m, n) > kStaticScratchBytes) return refuse(B200_E_TOO_LARGE);
+  void* scratch = nullptr;
+  const int rc = static_scratch(&scratch);
+  if (rc != 0) return finish(rc);
+  // Nothing in the array has to start at zero: stage 1 writes every partial that
+  // stage 2 reads, so whatever an earlier call left behind is overwritten first.
+  return column_sum_impl(dtype, x, out, m, n, ld, scratch, kStaticScratchBytes, static_cast<cudaStream_t>(stream));
 }

@@ -189,6 +189,35 @@ size_t b200_column_sum_workspace_bytes(int64_t m, int64_t n);
 int b200_column_sum(int32_t dtype, const void* x, float* out, int64_t m, int64_t n, int64_t ld,
                     void* workspace, size_t workspace_bytes, void* stream);
 
+/*
+ * b200_column_sum without any allocation and without caller scratch. It has no
+ * counterpart in the reference; it exists for hosts that cannot hand the library
+ * memory at call time: a serving process whose device memory is fully budgeted at
+ * start-up (weights, caches and activations planned to the last megabyte, so a
+ * later cudaMalloc may fail or is forbidden by policy), or a latency-critical loop
+ * that cannot afford the device-wide synchronisation an allocation or a free can
+ * imply. The partial sums live in a fixed array of B200_COLUMN_SUM_STATIC_MAX_BYTES
+ * inside the library's device image (so every GPU that loads the library holds
+ * that much memory until the process ends).
+ *
+ * - Shapes whose partial sums (b200_column_sum_workspace_bytes(m, n)) exceed the
+ *   array are refused with B200_E_TOO_LARGE; nothing runs. With the present
+ *   two-stage plan (at most 592 row chunks over 512-column strips) no shape needs
+ *   more than 1,212,416 bytes, so the 2 MiB array holds every shape; the check is
+ *   what keeps that true if the plan's constants change.
+ * - The first call on each device looks up the array's device address
+ *   (cudaGetSymbolAddress, with that device current). Make that first call outside
+ *   any stream capture; later calls do no set-up.
+ * - No cudaMalloc, cudaFree or other allocating routine is called, on any call.
+ * - All calls on a device share the one array and it keeps the last call's
+ *   contents (the kernels overwrite what they read, so no clearing is needed).
+ *   Two calls that may overlap on the GPU (different streams, or the same call
+ *   from two threads without ordering) race on it: order them.
+ */
+#define B200_COLUMN_SUM_STATIC_MAX_BYTES (2u << 20)
+int b200_column_sum_static(int32_t dtype, const void* x, float* out, int64_t m, int64_t n, int64_t ld,
+                           void* stream);
+
 /* Elementwise y = f(x) over `count` contiguous elements; y may equal x.
  * Replaces _relu_kernel, _leaky_relu_kernel, _scalar_mul_kernel (elementwise.py:14-41). */
 enum { B200_ELT_RELU = 0, B200_ELT_LEAKY_RELU = 1, B200_ELT_SCALAR_MUL = 2 };
