@@ -461,10 +461,11 @@ def run_reference(args: argparse.Namespace, workload: Workload, rank: int) -> No
 def main() -> None:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=30)
-    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--steps", type=int, default=200)
+    parser.add_argument("--warmup", type=int, default=20)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    parser.add_argument("--rows", type=int, default=0, help="rows per GPU of the c2/c4 workloads (default: the configuration's; smaller sizes are for profiler captures, not for reported numbers)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-e2e", action="store_true")
     args = parser.parse_args()
@@ -472,6 +473,8 @@ def main() -> None:
 
     rank, world, local_rank = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
     workload: Workload = WORKLOADS[args.workload]()
+    if args.rows > 0 and hasattr(workload, "M"):
+        workload.M = args.rows
     if args.impl == "reference":
         run_reference(args, workload, rank)
         return
@@ -498,13 +501,15 @@ def main() -> None:
             dist.barrier()
         torch.cuda.synchronize(device)
 
-    for i in range(warmup):
-        workload.step(i)
-    barrier()
+    # The clock sampler covers warm-up and timed region (100 ms period: a timed region
+    # of a few milliseconds alone would see no sample); the warm-up is the same load.
     sampler = ClockSampler(torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ else local_rank)
     if rank == 0:
         sampler.start()
-        time.sleep(0.15)
+        time.sleep(0.12)
+    for i in range(warmup):
+        workload.step(i)
+    barrier()
     launches_before = native.counters()["launches"]
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -574,7 +579,13 @@ def main() -> None:
 
 # DRAM bytes (read + write) per launch of each workload's dominant kernel, from
 # the ncu captures summarised under profiles/ (None until captured).
-TRAFFIC: dict[str, float | None] = {"c1": None, "c2": None, "c3": None, "c4": None, "c5": None}
+TRAFFIC: dict[str, float | None] = {
+    "c1": None,
+    "c2": 156.9e6,  # gemm_umma_bf16_kernel<2>: 111.9 MB read + 45.0 MB written (algorithmic 167.8 MB)
+    "c3": None,
+    "c4": 860.1e6,  # f32 softmax, scaled x4 from the 8192-row capture (134.26 MB read + 80.77 MB written)
+    "c5": None,
+}
 
 
 if __name__ == "__main__":
