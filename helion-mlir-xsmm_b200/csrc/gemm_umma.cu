@@ -67,7 +67,8 @@ struct UmmaParams {
   void* c;
   int64_t ldc, stride_c;
   int32_t out_bf16;
-  int32_t vec_store;  // rows of C are 16-byte aligned
+  int32_t vec_store;   // rows of C are 16-byte aligned
+  int32_t vec_params;  // bias / scale / shift start on 16-byte boundaries
   int32_t* status;
 };
 
@@ -265,6 +266,47 @@ __device__ __forceinline__ Tile tile_of(const UmmaParams& p, int64_t work, int r
   t.m0 = static_cast<int32_t>(r / p.tiles_n) * rows_per_tile + row_offset;
   t.n0 = static_cast<int32_t>(r % p.tiles_n) * p.block_n;
   return t;
+}
+
+// 32 consecutive entries of a bias / scale / shift vector as floats. `fast`: the
+// entries exist (col0 + 32 <= n) and start on a 16-byte boundary, so every lane
+// issues the same few vector loads (a broadcast from L1) instead of 32 scalar ones.
+__device__ __forceinline__ void load_vec32(const void* p, int64_t col0, int64_t n, bool bf16, bool scalar, bool fast,
+                                           float (&out)[32]) {
+  if (scalar) {
+    const float value = load_vec(p, 0, bf16);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) out[j] = value;
+  } else if (fast) {
+    if (bf16) {
+      const uint4* q = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p) + col0);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 w = __ldg(q + j);
+        out[8 * j] = __uint_as_float(w.x << 16);
+        out[8 * j + 1] = __uint_as_float(w.x & 0xffff0000u);
+        out[8 * j + 2] = __uint_as_float(w.y << 16);
+        out[8 * j + 3] = __uint_as_float(w.y & 0xffff0000u);
+        out[8 * j + 4] = __uint_as_float(w.z << 16);
+        out[8 * j + 5] = __uint_as_float(w.z & 0xffff0000u);
+        out[8 * j + 6] = __uint_as_float(w.w << 16);
+        out[8 * j + 7] = __uint_as_float(w.w & 0xffff0000u);
+      }
+    } else {
+      const float4* q = reinterpret_cast<const float4*>(static_cast<const float*>(p) + col0);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float4 w = __ldg(q + j);
+        out[4 * j] = w.x;
+        out[4 * j + 1] = w.y;
+        out[4 * j + 2] = w.z;
+        out[4 * j + 3] = w.w;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) out[j] = load_vec(p, (col0 + j < n) ? col0 + j : n - 1, bf16);
+  }
 }
 
 __device__ __forceinline__ void activate32(int act, float alpha, float (&v)[32]) {
@@ -509,14 +551,24 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
           }
           if (last) {
-            if (p.epi.bias || p.epi.scale || p.epi.shift) {
+            const bool vec_fast = full_chunk && p.vec_params;
+            if (p.epi.bias) {
+              float w[32];
+              load_vec32(p.epi.bias, col0, p.n, p.epi.vec_bf16, p.epi.bias_scalar, vec_fast, w);
 #pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                const int64_t col = (col0 + j < p.n) ? col0 + j : p.n - 1;
-                if (p.epi.bias) v[j] += load_vec(p.epi.bias, p.epi.bias_scalar ? 0 : col, p.epi.vec_bf16);
-                if (p.epi.scale) v[j] *= load_vec(p.epi.scale, p.epi.scale_scalar ? 0 : col, p.epi.vec_bf16);
-                if (p.epi.shift) v[j] += load_vec(p.epi.shift, p.epi.shift_scalar ? 0 : col, p.epi.vec_bf16);
-              }
+              for (int j = 0; j < 32; ++j) v[j] += w[j];
+            }
+            if (p.epi.scale) {
+              float w[32];
+              load_vec32(p.epi.scale, col0, p.n, p.epi.vec_bf16, p.epi.scale_scalar, vec_fast, w);
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] *= w[j];
+            }
+            if (p.epi.shift) {
+              float w[32];
+              load_vec32(p.epi.shift, col0, p.n, p.epi.vec_bf16, p.epi.shift_scalar, vec_fast, w);
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] += w[j];
             }
             activate32(p.epi.act, p.epi.alpha, v);
           }
@@ -768,6 +820,7 @@ int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* parti
   const size_t out_size = p.out_bf16 ? 2 : 4;
   p.vec_store = aligned(p.c, 16) && (p.ldc * out_size) % 16 == 0 && (p.stride_c * out_size) % 16 == 0 &&
                 (p.psplit_stride * out_size) % 16 == 0;
+  p.vec_params = aligned(epi.bias, 16) && aligned(epi.scale, 16) && aligned(epi.shift, 16);
   p.status = kernel_status_word();
 
   std::call_once(g_attr_once[dev.device], [] {
