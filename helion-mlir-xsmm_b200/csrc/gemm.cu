@@ -2,8 +2,9 @@
 //
 // Paths, in order of preference:
 //   tensor cores  bf16 operands whose rows TMA can describe (16-byte aligned bases
-//                 and pitches), plain ROW/COL layouts directly; the two VNNI layouts
-//                 of B through an unpack to K-contiguous [N, K] in the caller's workspace
+//                 and pitches), plain ROW/COL layouts directly; blocked A and the
+//                 blocked / VNNI layouts of B through unpacks to row-major in the
+//                 caller's workspace
 //   FFMA          everything else (f32, odd pitches, blocked layouts), exact f32
 // The choice mirrors the dispatcher of helion_mlir_utils/matmul.py:1446-1570
 // (bf16 -> fused kernel, f32 -> split-K / fused / blocked) with the CPU tile
@@ -29,7 +30,9 @@ struct Resolved {
   int64_t k_pad;        // K as the packed layouts pad it
   int64_t n_pad;        // N as the packed B layout pads it
   bool b_is_vnni;
-  size_t unpack_bytes;  // workspace for B unpacked to [n_pad, k_pad] bf16
+  int64_t m_pad;          // M as the blocked A layout pads it
+  size_t unpack_a_bytes;  // workspace for a blocked A unpacked to [m_pad, k_pad] bf16
+  size_t unpack_bytes;    // workspace for a packed B unpacked to [n_pad, k_pad] bf16
   size_t partial_bytes; // workspace for parallel split-K partials
 };
 
@@ -97,19 +100,34 @@ int validate(const b200_gemm_desc* d, Resolved* r) {
                         d->bias_n == 1,    d->scale_n == 1,   d->shift_n == 1,
                         d->vec_dtype == B200_BF16, d->epilogue, d->alpha};
   r->b_is_vnni = d->b_layout == B200_LAYOUT_BLOCKED_VNNI || d->b_layout == B200_LAYOUT_VNNI_PANELS;
-  r->unpack_bytes = r->b_is_vnni ? static_cast<size_t>(round_up(r->n_pad * k32 * 2, 256)) : 0;
+  r->m_pad = round_up(d->m, 32);
+  const bool bf16 = d->dtype == B200_BF16;
+  r->unpack_a_bytes =
+      (bf16 && d->a_layout == B200_LAYOUT_BLOCKED) ? static_cast<size_t>(round_up(r->m_pad * k32 * 2, 256)) : 0;
+  r->unpack_bytes = (bf16 && d->b_layout >= B200_LAYOUT_BLOCKED)
+                        ? static_cast<size_t>(round_up(r->n_pad * k32 * 2, 256))
+                        : 0;
   r->partial_bytes =
       d->split_k > 1 ? static_cast<size_t>(d->split_k) * d->batch * d->m * d->n * sizeof(float) : 0;
   return 0;
 }
 
-// The descriptor the tensor-core kernel sees once a VNNI B has been unpacked.
-b200_gemm_desc unpacked_desc(const b200_gemm_desc& d, const Resolved& r, void* unpacked) {
+// The descriptor the tensor-core kernel sees once packed operands have been
+// unpacked: A as row-major [m_pad, k_pad], B as K-contiguous [n_pad, k_pad].
+b200_gemm_desc unpacked_desc(const b200_gemm_desc& d, const Resolved& r, void* a_unpacked, void* b_unpacked) {
   b200_gemm_desc u = d;
-  u.b = unpacked;
-  u.b_layout = B200_LAYOUT_COL;
-  u.ldb = r.k_pad;
-  u.stride_b = r.n_pad * r.k_pad;
+  if (r.unpack_a_bytes) {
+    u.a = a_unpacked;
+    u.a_layout = B200_LAYOUT_ROW;
+    u.lda = r.k_pad;
+    u.stride_a = r.m_pad * r.k_pad;
+  }
+  if (r.unpack_bytes) {
+    u.b = b_unpacked;
+    u.b_layout = B200_LAYOUT_COL;
+    u.ldb = r.k_pad;
+    u.stride_b = r.n_pad * r.k_pad;
+  }
   return u;
 }
 
@@ -120,20 +138,17 @@ Path choose(const b200_gemm_desc& d, const Resolved& r, int* why) {
   *why = 0;
   if (d.force_kernel == 2) return kPathSimt;
   if (d.k == 0) return kPathSimt;
-  if (r.b_is_vnni) {
-    if (d.a_layout > B200_LAYOUT_COL) {
-      *why = B200_E_ARG;
-      return kPathSimt;
-    }
+  if (r.unpack_a_bytes || r.unpack_bytes) {
     if (d.batch != 1) {
       *why = B200_E_SHAPE;
       return kPathSimt;
     }
-    if (!d.workspace || d.workspace_bytes < r.unpack_bytes || !aligned(d.workspace, 256)) {
+    if (!d.workspace || d.workspace_bytes < r.unpack_a_bytes + r.unpack_bytes || !aligned(d.workspace, 256)) {
       *why = B200_E_WORKSPACE;
       return kPathSimt;
     }
-    b200_gemm_desc u = unpacked_desc(d, r, d.workspace);
+    uint8_t* ws = static_cast<uint8_t*>(d.workspace);
+    b200_gemm_desc u = unpacked_desc(d, r, ws, ws + r.unpack_a_bytes);
     *why = umma_supports(u);
     return *why == 0 ? kPathUmmaUnpack : kPathSimt;
   }
@@ -149,7 +164,7 @@ using namespace b200;
 extern "C" size_t b200_gemm_workspace_bytes(const b200_gemm_desc* desc) {
   Resolved r{};
   if (validate(desc, &r) != 0 || desc->m == 0 || desc->n == 0) return 0;
-  return r.unpack_bytes + r.partial_bytes;
+  return r.unpack_a_bytes + r.unpack_bytes + r.partial_bytes;
 }
 
 extern "C" int b200_gemm(const b200_gemm_desc* desc, void* stream) {
@@ -165,14 +180,15 @@ extern "C" int b200_gemm(const b200_gemm_desc* desc, void* stream) {
   const Path path = choose(d, r, &why);
   if (path == kPathSimt && d.force_kernel != 0 && d.force_kernel != 2) return refuse(why ? why : B200_E_ARG);
 
-  // Workspace carve-up: [unpacked B][split-K partials].
+  // Workspace carve-up: [unpacked A][unpacked B][split-K partials].
   uint8_t* ws = static_cast<uint8_t*>(d.workspace);
   size_t ws_left = d.workspace ? d.workspace_bytes : 0;
-  void* unpacked = nullptr;
+  void *a_unpacked = nullptr, *b_unpacked = nullptr;
   if (path == kPathUmmaUnpack) {
-    unpacked = ws;
-    ws += r.unpack_bytes;
-    ws_left -= r.unpack_bytes;
+    a_unpacked = ws;
+    b_unpacked = ws + r.unpack_a_bytes;
+    ws += r.unpack_a_bytes + r.unpack_bytes;
+    ws_left -= r.unpack_a_bytes + r.unpack_bytes;
   }
   float* partials = nullptr;
   if (d.split_k > 1 && ws_left >= r.partial_bytes && ws_left > 0 && aligned(ws, 16)) partials = reinterpret_cast<float*>(ws);
@@ -181,11 +197,19 @@ extern "C" int b200_gemm(const b200_gemm_desc* desc, void* stream) {
 
   if (d.split_k > 1 && !partials && d.out_dtype != B200_F32) return refuse(B200_E_WORKSPACE);
   if (path == kPathUmmaUnpack) {
-    const int kind =
-        d.b_layout == B200_LAYOUT_VNNI_PANELS ? B200_UNPACK_B_VNNI_PANELS_TO_NK : B200_UNPACK_B_VNNI_TO_NK;
-    const int rc = b200_pack(kind, B200_BF16, d.b, 0, 0, 0, unpacked, r.n_pad, r.k_pad, d.b_panel, stream);
-    if (rc != 0) return rc;
-    const b200_gemm_desc u = unpacked_desc(d, r, unpacked);
+    if (r.unpack_a_bytes) {
+      const int rc =
+          b200_pack(B200_UNPACK_A_BLOCKED_TO_MK, B200_BF16, d.a, 0, 0, 0, a_unpacked, r.m_pad, r.k_pad, 0, stream);
+      if (rc != 0) return rc;
+    }
+    if (r.unpack_bytes) {
+      const int kind = d.b_layout == B200_LAYOUT_VNNI_PANELS  ? B200_UNPACK_B_VNNI_PANELS_TO_NK
+                       : d.b_layout == B200_LAYOUT_BLOCKED_VNNI ? B200_UNPACK_B_VNNI_TO_NK
+                                                                : B200_UNPACK_B_BLOCKED_TO_NK;
+      const int rc = b200_pack(kind, B200_BF16, d.b, 0, 0, 0, b_unpacked, r.n_pad, r.k_pad, d.b_panel, stream);
+      if (rc != 0) return rc;
+    }
+    const b200_gemm_desc u = unpacked_desc(d, r, a_unpacked, b_unpacked);
     return run_gemm_umma(u, r.epi, partials, s);
   }
   return run_gemm_umma(d, r.epi, partials, s);
@@ -207,9 +231,11 @@ extern "C" int b200_gemm_explain(const b200_gemm_desc* desc, char* buf, size_t b
              desc->force_kernel == 2 ? "forced" : b200_strerror(why));
     return (desc->force_kernel != 0 && desc->force_kernel != 2) ? (why ? why : B200_E_ARG) : 0;
   }
-  const b200_gemm_desc u = path == kPathUmmaUnpack ? unpacked_desc(*desc, r, desc->workspace) : *desc;
+  uint8_t* ws = static_cast<uint8_t*>(desc->workspace);
+  const b200_gemm_desc u =
+      path == kPathUmmaUnpack ? unpacked_desc(*desc, r, ws, ws ? ws + r.unpack_a_bytes : nullptr) : *desc;
   char inner[200];
   explain_gemm_umma(u, inner, sizeof inner);
-  snprintf(buf, buf_len, "%s%s", path == kPathUmmaUnpack ? "unpack_vnni + " : "", inner);
+  snprintf(buf, buf_len, "%s%s", path == kPathUmmaUnpack ? "unpack to row-major + " : "", inner);
   return 0;
 }

@@ -152,6 +152,43 @@ __global__ void __launch_bounds__(256) unpack_vnni_kernel(const uint32_t* __rest
   }
 }
 
+// Blocked A [Mp/32][Kp/32][32][32] -> row-major [Mp][Kp]: 32-element row segments
+// are contiguous on both sides; one thread moves 16 bytes.
+template <typename T>
+__global__ void __launch_bounds__(256) unpack_a_blocked_kernel(const T* __restrict__ src, T* __restrict__ dst,
+                                                               int64_t m_pad, int64_t k_pad) {
+  constexpr int W = 16 / sizeof(T);
+  const int64_t units = m_pad * k_pad / W;
+  const int64_t kblocks = k_pad >> 5;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t u = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; u < units; u += stride) {
+    const int64_t e = u * W, m = e / k_pad, k = e - m * k_pad;
+    const int64_t off = (((m >> 5) * kblocks + (k >> 5)) << 10) + ((m & 31) << 5) + (k & 31);
+    st_stream16(dst + e, ld_stream16(src + off));
+  }
+}
+
+// Blocked B [Np/32][Kp/32][32 k][32 n] -> [Np][Kp]: one 32x32 block per CTA,
+// transposed through shared memory.
+template <typename T>
+__global__ void __launch_bounds__(256) unpack_b_blocked_kernel(const T* __restrict__ src, T* __restrict__ dst,
+                                                               int64_t n_pad, int64_t k_pad) {
+  __shared__ T tile[32][33];
+  const int64_t kblocks = k_pad >> 5;
+  const int64_t block = blockIdx.x;
+  const int64_t nb = block / kblocks, kb = block - nb * kblocks;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const T* s = src + (block << 10);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) tile[ty + 8 * i][tx] = s[(ty + 8 * i) * 32 + tx];  // [k][n]
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int n = ty + 8 * i;
+    dst[(nb * 32 + n) * k_pad + kb * 32 + tx] = tile[tx][n];
+  }
+}
+
 template <typename T, int KIND, bool ROWS>
 int launch_pack(const PackParams& p, cudaStream_t stream) {
   const DeviceInfo& dev = device_info();
@@ -226,6 +263,33 @@ extern "C" int b200_pack(int32_t kind, int32_t dtype, const void* src, int64_t r
     else
       unpack_vnni_kernel<false><<<grid, 256, 0, s>>>(static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst),
                                                      rows_pad, pairs, panel);
+    return launched();
+  }
+
+  if (kind == B200_UNPACK_A_BLOCKED_TO_MK || kind == B200_UNPACK_B_BLOCKED_TO_NK) {
+    // rows_pad x cols_pad are Mp x Kp (A) or Np x Kp (B) of the row-major destination.
+    if (rows_pad % 32 || cols_pad % 32) return refuse(B200_E_SHAPE);
+    if (!aligned(src, 16) || !aligned(dst, 16)) return refuse(B200_E_ALIGN);
+    const int64_t blocks = (rows_pad >> 5) * (cols_pad >> 5);
+    if (kind == B200_UNPACK_A_BLOCKED_TO_MK) {
+      const int64_t units = rows_pad * cols_pad / (16 / static_cast<int64_t>(dtype_size(dtype)));
+      const int64_t wanted = ceil_div(units, 256), resident = static_cast<int64_t>(device_info().sm_count) * 16;
+      const unsigned grid = static_cast<unsigned>(wanted < resident ? wanted : resident);
+      if (dtype == B200_F32)
+        unpack_a_blocked_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(src), static_cast<float*>(dst),
+                                                            rows_pad, cols_pad);
+      else
+        unpack_a_blocked_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(
+            static_cast<const __nv_bfloat16*>(src), static_cast<__nv_bfloat16*>(dst), rows_pad, cols_pad);
+    } else {
+      if (blocks > 0x7fffffff) return refuse(B200_E_SHAPE);
+      if (dtype == B200_F32)
+        unpack_b_blocked_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+            static_cast<const float*>(src), static_cast<float*>(dst), rows_pad, cols_pad);
+      else
+        unpack_b_blocked_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+            static_cast<const __nv_bfloat16*>(src), static_cast<__nv_bfloat16*>(dst), rows_pad, cols_pad);
+    }
     return launched();
   }
 

@@ -41,7 +41,9 @@ LAYOUT_ROW, LAYOUT_COL, LAYOUT_BLOCKED, LAYOUT_BLOCKED_VNNI, LAYOUT_VNNI_PANELS 
     PACK_B_VNNI_PANELS_T,
     UNPACK_B_VNNI_TO_NK,
     UNPACK_B_VNNI_PANELS_TO_NK,
-) = range(10)
+    UNPACK_A_BLOCKED_TO_MK,
+    UNPACK_B_BLOCKED_TO_NK,
+) = range(12)
 NORM_EXTRA_NONE, NORM_EXTRA_ADD, NORM_EXTRA_MUL = range(3)
 REDUCE_ROW_SUM, REDUCE_ROW_DOT, REDUCE_MATVEC = range(3)
 ELT_RELU, ELT_LEAKY_RELU, ELT_SCALAR_MUL = range(3)

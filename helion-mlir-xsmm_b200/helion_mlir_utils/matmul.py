@@ -275,9 +275,9 @@ class GemmPlan:
         self.parallel_split = parallel_split
         self.launches = 0
         d = desc
-        self._wants_workspace = d.b_layout in (native.LAYOUT_BLOCKED_VNNI, native.LAYOUT_VNNI_PANELS) or (
-            d.split_k > 1 and parallel_split
-        )
+        # packed bf16 operands are unpacked into scratch for the tensor cores
+        packed = d.dtype == native.BF16 and (d.a_layout == native.LAYOUT_BLOCKED or d.b_layout >= native.LAYOUT_BLOCKED)
+        self._wants_workspace = packed or (d.split_k > 1 and parallel_split)
 
     def run(self, a: Tensor, b: Tensor, bias: Tensor | None = None, scale: Tensor | None = None,
             shift: Tensor | None = None, out: Tensor | None = None) -> Tensor:

@@ -142,7 +142,9 @@ enum {
   /* inverse conversions used by the tensor-core GEMM for VNNI operands */
   B200_UNPACK_B_VNNI_TO_NK = 8,        /* [Np/32,Kp/32,16,32,2] -> [Np,Kp] row-major (K contiguous) */
   B200_UNPACK_B_VNNI_PANELS_TO_NK = 9, /* [Np/P,Kp/2,P,2] -> [Np,Kp] */
-  B200_PACK_COUNT_ = 10
+  B200_UNPACK_A_BLOCKED_TO_MK = 10,    /* [Mp/32,Kp/32,32,32] -> [Mp,Kp] row-major */
+  B200_UNPACK_B_BLOCKED_TO_NK = 11,    /* [Np/32,Kp/32,32(k),32(n)] -> [Np,Kp] row-major (K contiguous) */
+  B200_PACK_COUNT_ = 12
 };
 
 /* src: `rows` x `cols` row-major with leading dimension `ld` (elements);
