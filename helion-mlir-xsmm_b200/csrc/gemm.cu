@@ -5,7 +5,8 @@
 //                 and pitches), plain ROW/COL layouts directly; blocked A and the
 //                 blocked / VNNI layouts of B through unpacks to row-major in the
 //                 caller's workspace
-//   FFMA          everything else (f32, odd pitches, blocked layouts), exact f32
+//                 f32 operands of plain layouts as a six-term bf16 split over a 6x longer K
+//   FFMA          everything else (small or oddly pitched f32, f32 blocked layouts), exact f32
 // The choice mirrors the dispatcher of helion_mlir_utils/matmul.py:1446-1570
 // (bf16 -> fused kernel, f32 -> split-K / fused / blocked) with the CPU tile
 // heuristics replaced by the SM count; block_sizes arrive as tile_m/n/k hints.
@@ -22,7 +23,23 @@ int explain_gemm_umma(const b200_gemm_desc& d, char* buf, size_t len);
 int run_gemm_simt(const b200_gemm_desc& d, const GemmOperand& a, const GemmOperand& b, const GemmEpilogue& epi,
                   int splits, float* workspace, cudaStream_t stream);
 
+int launch_split_f32(const float* src, void* dst, int64_t rows, int64_t cols, int64_t ld, bool is_b, bool along_cols,
+                     cudaStream_t stream);
+
 namespace {
+
+// f32 operands on the tensor cores: each f32 value is split into three bf16 parts
+// and the six largest cross products are summed by one bf16 GEMM over a six times
+// longer K (the bf16 analogue of 3xTF32; products of bf16 parts are exact in f32).
+// The tensor core's f32 accumulation truncates, a bias that grows with the length
+// and magnitude of a running sum (measured: relative Frobenius error 1.0e-6 at
+// K=1024, 4.4e-6 at K=4096 against the 1e-5 bar). So long sums are cut into chunks
+// of kSplitChunkK widened-K elements that the epilogue adds in f32 (serial split-K),
+// and K above kSplitMaxK stays on the exact FFMA kernel.
+constexpr int kSplitTerms = 6;
+constexpr int64_t kSplitChunkK = 2048;
+constexpr int64_t kSplitMaxK = 4096;
+constexpr int64_t kSplitMinWork = int64_t(1) << 24;  // m*n*k below this stays on the FFMA kernel
 
 struct Resolved {
   GemmOperand a, b;
@@ -34,7 +51,19 @@ struct Resolved {
   size_t unpack_a_bytes;  // workspace for a blocked A unpacked to [m_pad, k_pad] bf16
   size_t unpack_bytes;    // workspace for a packed B unpacked to [n_pad, k_pad] bf16
   size_t partial_bytes; // workspace for parallel split-K partials
+  size_t split_a_bytes, split_b_bytes;  // workspace for the six-fold bf16 split of f32 operands (0: not applicable)
 };
+
+// Whether the f32 GEMM `d` can run as a widened bf16 GEMM (layouts TMA can describe).
+bool f32_split_applies(const b200_gemm_desc& d) {
+  if (d.dtype != B200_F32 || d.a_layout > B200_LAYOUT_COL || d.b_layout > B200_LAYOUT_COL) return false;
+  if (d.batch != 1 || d.split_k > 1 || d.k < 1 || d.k > kSplitMaxK) return false;
+  if (d.m * d.n * d.k < kSplitMinWork) return false;
+  // row pitches of the widened operands must be multiples of 16 bytes
+  const bool a_ok = d.a_layout == B200_LAYOUT_ROW ? d.k % 4 == 0 : d.m % 8 == 0;
+  const bool b_ok = d.b_layout == B200_LAYOUT_COL ? d.k % 4 == 0 : d.n % 8 == 0;
+  return a_ok && b_ok && d.k * kSplitTerms < (int64_t(1) << 30);
+}
 
 int validate(const b200_gemm_desc* d, Resolved* r) {
   if (!d) return B200_E_NULL;
@@ -109,6 +138,11 @@ int validate(const b200_gemm_desc* d, Resolved* r) {
                         : 0;
   r->partial_bytes =
       d->split_k > 1 ? static_cast<size_t>(d->split_k) * d->batch * d->m * d->n * sizeof(float) : 0;
+  r->split_a_bytes = r->split_b_bytes = 0;
+  if (f32_split_applies(*d)) {
+    r->split_a_bytes = static_cast<size_t>(round_up(d->m * d->k * kSplitTerms * 2, 256));
+    r->split_b_bytes = static_cast<size_t>(round_up(d->n * d->k * kSplitTerms * 2, 256));
+  }
   return 0;
 }
 
@@ -131,7 +165,24 @@ b200_gemm_desc unpacked_desc(const b200_gemm_desc& d, const Resolved& r, void* a
   return u;
 }
 
-enum Path { kPathUmma, kPathUmmaUnpack, kPathSimt };
+enum Path { kPathUmma, kPathUmmaUnpack, kPathUmmaSplitF32, kPathSimt };
+
+// The bf16 GEMM over the widened K that stands for the f32 GEMM `d`.
+b200_gemm_desc split_desc(const b200_gemm_desc& d, void* a_wide, void* b_wide) {
+  b200_gemm_desc u = d;
+  u.dtype = B200_BF16;
+  u.a = a_wide;
+  u.b = b_wide;
+  u.k = d.k * kSplitTerms;
+  u.lda = d.a_layout == B200_LAYOUT_ROW ? u.k : d.m;  // [M, 6K] or [6K, M]
+  u.ldb = d.b_layout == B200_LAYOUT_COL ? u.k : d.n;  // [N, 6K] or [6K, N]
+  // chunks of the widened K are added in f32 by the epilogue (needs an f32 result)
+  u.split_k = d.out_dtype == B200_F32 ? static_cast<int32_t>(ceil_div(u.k, kSplitChunkK)) : 0;
+  if (u.split_k < 2) u.split_k = 0;
+  u.workspace = nullptr;
+  u.workspace_bytes = 0;
+  return u;
+}
 
 // Chooses the path; `*why` gets the refusal of the tensor-core path when it is not taken.
 Path choose(const b200_gemm_desc& d, const Resolved& r, int* why) {
@@ -152,6 +203,15 @@ Path choose(const b200_gemm_desc& d, const Resolved& r, int* why) {
     *why = umma_supports(u);
     return *why == 0 ? kPathUmmaUnpack : kPathSimt;
   }
+  if (r.split_a_bytes) {
+    if (!d.workspace || d.workspace_bytes < r.split_a_bytes + r.split_b_bytes || !aligned(d.workspace, 256)) {
+      *why = B200_E_WORKSPACE;
+      return kPathSimt;
+    }
+    uint8_t* ws = static_cast<uint8_t*>(d.workspace);
+    *why = umma_supports(split_desc(d, ws, ws + r.split_a_bytes));
+    return *why == 0 ? kPathUmmaSplitF32 : kPathSimt;
+  }
   *why = umma_supports(d);
   return *why == 0 ? kPathUmma : kPathSimt;
 }
@@ -164,7 +224,7 @@ using namespace b200;
 extern "C" size_t b200_gemm_workspace_bytes(const b200_gemm_desc* desc) {
   Resolved r{};
   if (validate(desc, &r) != 0 || desc->m == 0 || desc->n == 0) return 0;
-  return r.unpack_a_bytes + r.unpack_bytes + r.partial_bytes;
+  return r.unpack_a_bytes + r.unpack_bytes + r.partial_bytes + r.split_a_bytes + r.split_b_bytes;
 }
 
 extern "C" int b200_gemm(const b200_gemm_desc* desc, void* stream) {
@@ -194,6 +254,18 @@ extern "C" int b200_gemm(const b200_gemm_desc* desc, void* stream) {
   if (d.split_k > 1 && ws_left >= r.partial_bytes && ws_left > 0 && aligned(ws, 16)) partials = reinterpret_cast<float*>(ws);
 
   if (path == kPathSimt) return run_gemm_simt(d, r.a, r.b, r.epi, d.split_k, partials, s);
+
+  if (path == kPathUmmaSplitF32) {
+    uint8_t* wide = static_cast<uint8_t*>(d.workspace);
+    const bool a_cols = d.a_layout == B200_LAYOUT_ROW, b_cols = d.b_layout == B200_LAYOUT_COL;
+    int rc = launch_split_f32(static_cast<const float*>(d.a), wide, a_cols ? d.m : d.k, a_cols ? d.k : d.m, d.lda,
+                              false, a_cols, s);
+    if (rc == 0)
+      rc = launch_split_f32(static_cast<const float*>(d.b), wide + r.split_a_bytes, b_cols ? d.n : d.k,
+                            b_cols ? d.k : d.n, d.ldb, true, b_cols, s);
+    if (rc != 0) return finish(rc);
+    return run_gemm_umma(split_desc(d, wide, wide + r.split_a_bytes), r.epi, nullptr, s);
+  }
 
   if (d.split_k > 1 && !partials && d.out_dtype != B200_F32) return refuse(B200_E_WORKSPACE);
   if (path == kPathUmmaUnpack) {
@@ -232,10 +304,15 @@ extern "C" int b200_gemm_explain(const b200_gemm_desc* desc, char* buf, size_t b
     return (desc->force_kernel != 0 && desc->force_kernel != 2) ? (why ? why : B200_E_ARG) : 0;
   }
   uint8_t* ws = static_cast<uint8_t*>(desc->workspace);
-  const b200_gemm_desc u =
-      path == kPathUmmaUnpack ? unpacked_desc(*desc, r, ws, ws ? ws + r.unpack_a_bytes : nullptr) : *desc;
+  b200_gemm_desc u = *desc;
+  if (path == kPathUmmaUnpack) u = unpacked_desc(*desc, r, ws, ws ? ws + r.unpack_a_bytes : nullptr);
+  if (path == kPathUmmaSplitF32) u = split_desc(*desc, ws, ws + r.split_a_bytes);
   char inner[200];
   explain_gemm_umma(u, inner, sizeof inner);
-  snprintf(buf, buf_len, "%s%s", path == kPathUmmaUnpack ? "unpack to row-major + " : "", inner);
+  snprintf(buf, buf_len, "%s%s",
+           path == kPathUmmaUnpack     ? "unpack to row-major + "
+           : path == kPathUmmaSplitF32 ? "f32 as 6 bf16 cross products (K x6) + "
+                                       : "",
+           inner);
   return 0;
 }

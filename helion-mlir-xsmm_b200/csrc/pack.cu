@@ -189,6 +189,39 @@ __global__ void __launch_bounds__(256) unpack_b_blocked_kernel(const T* __restri
   }
 }
 
+// f32 -> three bf16 parts x = x1 + x2 + x3 (each the bf16 rounding of what is left),
+// written six times side by side along the contraction dimension so that one bf16
+// GEMM over the widened K sums the six largest cross products of an f32 product:
+//   A operand parts (3,2,1,2,1,1), B operand parts (1,2,3,1,2,1)
+//   -> a3 b1 + a2 b2 + a1 b3 + a2 b1 + a1 b2 + a1 b1, smallest terms first so that
+//      they are not absorbed by a large running sum.
+// along_cols: the contraction dimension is the column dimension (copies side by
+// side in a row, out [rows, 6*cols]); else the row dimension (out [6*rows, cols]).
+__global__ void __launch_bounds__(256) split_f32_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst,
+                                                        int64_t rows, int64_t cols, int64_t ld, int is_b,
+                                                        int along_cols) {
+  const int64_t total = rows * cols;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t r = i / cols, c = i - r * cols;
+    const float x = src[r * ld + c];
+    __nv_bfloat16 part[3];
+    part[0] = __float2bfloat16_rn(x);
+    const float r1 = x - __bfloat162float(part[0]);
+    part[1] = __float2bfloat16_rn(r1);
+    part[2] = __float2bfloat16_rn(r1 - __bfloat162float(part[1]));
+    const int pattern_a[6] = {2, 1, 0, 1, 0, 0}, pattern_b[6] = {0, 1, 2, 0, 1, 0};
+#pragma unroll
+    for (int t = 0; t < 6; ++t) {
+      const __nv_bfloat16 v = part[is_b ? pattern_b[t] : pattern_a[t]];
+      if (along_cols)
+        dst[r * (6 * cols) + t * cols + c] = v;
+      else
+        dst[(t * rows + r) * cols + c] = v;
+    }
+  }
+}
+
 template <typename T, int KIND, bool ROWS>
 int launch_pack(const PackParams& p, cudaStream_t stream) {
   const DeviceInfo& dev = device_info();
@@ -231,6 +264,17 @@ int run_pack(int kind, const PackParams& p, cudaStream_t stream) {
 }
 
 }  // namespace
+
+// Widens an f32 GEMM operand into its six-fold bf16 split (see split_f32_kernel).
+int launch_split_f32(const float* src, void* dst, int64_t rows, int64_t cols, int64_t ld, bool is_b, bool along_cols,
+                     cudaStream_t stream) {
+  const int64_t wanted = ceil_div(rows * cols, 256), resident = static_cast<int64_t>(device_info().sm_count) * 16;
+  const unsigned grid = static_cast<unsigned>(wanted < resident ? (wanted > 0 ? wanted : 1) : resident);
+  split_f32_kernel<<<grid, 256, 0, stream>>>(src, static_cast<__nv_bfloat16*>(dst), rows, cols, ld, is_b ? 1 : 0,
+                                             along_cols ? 1 : 0);
+  return check_launch();
+}
+
 }  // namespace b200
 
 using namespace b200;

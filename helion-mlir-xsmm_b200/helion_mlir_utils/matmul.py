@@ -277,7 +277,9 @@ class GemmPlan:
         d = desc
         # packed bf16 operands are unpacked into scratch for the tensor cores
         packed = d.dtype == native.BF16 and (d.a_layout == native.LAYOUT_BLOCKED or d.b_layout >= native.LAYOUT_BLOCKED)
-        self._wants_workspace = packed or (d.split_k > 1 and parallel_split)
+        # f32 operands of plain layouts run as a widened bf16 GEMM built in scratch
+        widened = d.dtype == native.F32 and d.a_layout <= native.LAYOUT_COL and d.b_layout <= native.LAYOUT_COL
+        self._wants_workspace = packed or widened or (d.split_k > 1 and parallel_split)
 
     def run(self, a: Tensor, b: Tensor, bias: Tensor | None = None, scale: Tensor | None = None,
             shift: Tensor | None = None, out: Tensor | None = None) -> Tensor:
