@@ -51,6 +51,11 @@ from .reduction import matvec
 from .reduction import row_dot
 from .reduction import row_sum
 from .reduction import supports_matvec
+from .sharding import column_sharded_linear
+from .sharding import gather_rows
+from .sharding import row_sharded
+from .sharding import shard_bounds
+from .sharding import shard_rows
 
 __all__ = [
     "CACHE_PREPACKED_WEIGHTS_ENV",
@@ -59,7 +64,9 @@ __all__ = [
     "add_extra",
     "bmm",
     "cache_prepacked_weights",
+    "column_sharded_linear",
     "column_sum",
+    "gather_rows",
     "gelu_tanh",
     "group_norm",
     "identity_epilogue",
@@ -87,8 +94,11 @@ __all__ = [
     "relu",
     "rms_norm",
     "row_dot",
+    "row_sharded",
     "row_sum",
     "scalar_mul",
+    "shard_bounds",
+    "shard_rows",
     "softmax",
     "supports",
     "supports_matvec",
