@@ -11,6 +11,7 @@ gets an exception.
 
 from __future__ import annotations
 
+import contextlib
 import ctypes
 from ctypes import c_char_p
 from ctypes import c_float
@@ -251,6 +252,18 @@ def stream_ptr(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
+_NO_SWITCH = contextlib.nullcontext()
+
+
+def on_device(device: torch.device):
+    """Context in which ``device`` is current: a no-op when it already is (the usual
+    case; entering ``torch.cuda.device`` costs microseconds per call)."""
+    index = device.index
+    if index is None or index == torch.cuda.current_device():
+        return _NO_SWITCH
+    return torch.cuda.device(device)
+
+
 def require_cuda(*tensors: torch.Tensor | None) -> torch.device:
     device = None
     for t in tensors:
@@ -276,6 +289,6 @@ def kernel_status(device: torch.device | None = None) -> int:
     """Error bits left by kernels whose bounded waits ran out (0: none). Synchronises."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
     value = c_int32(0)
-    with torch.cuda.device(device):
+    with on_device(device):
         check("b200_read_kernel_status", module().b200_read_kernel_status(stream_ptr(device), ctypes.byref(value)))
     return int(value.value)

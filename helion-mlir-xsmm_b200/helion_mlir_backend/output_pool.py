@@ -20,9 +20,11 @@ New on the device: reuse is stream-aware. A freed block is handed to a request
 on the stream that last used it at once, and to another stream only after the
 work that was pending at free time has finished (an event recorded at free).
 
-The storage hook: ``torch.as_tensor`` keeps an object exposing
-``__cuda_array_interface__`` alive until the storage dies; that object's
-``__del__`` returns the block.
+The storage hook: a block is wrapped once as a torch storage (``torch.as_tensor``
+over an object exposing ``__cuda_array_interface__``, whose ``__del__`` returns the
+memory to the library's pool when the storage finally dies) and that storage is
+kept and re-shaped for every tensor handed out; a block is free when the pool
+holds the only reference to its storage.
 """
 
 from __future__ import annotations
@@ -30,6 +32,7 @@ from __future__ import annotations
 import ctypes
 import math
 import os
+import threading
 import warnings
 
 import torch
@@ -59,7 +62,7 @@ _DTYPES = frozenset(
 
 
 class _Lease:
-    """A pool block on loan to one tensor storage."""
+    """A block of the library's device pool on loan to one torch storage."""
 
     __slots__ = ("__cuda_array_interface__", "device", "pointer")
 
@@ -79,15 +82,39 @@ class _Lease:
         # interpreter exit): never raises.
         try:
             stream = torch.cuda.current_stream(self.device).cuda_stream
-            with torch.cuda.device(self.device):
+            with native.on_device(self.device):
                 native.module().b200_pool_free(self.pointer, stream)
         except Exception:  # noqa: BLE001
             pass
 
 
+class _Block:
+    """A pool block wrapped once as a torch storage and handed out many times.
+
+    Wrapping device memory as a storage (``torch.as_tensor`` over the lease) costs
+    tens of microseconds; shaping a tensor onto an existing storage costs two. So
+    the storage is kept, and a block is free exactly when this record holds the
+    only reference to it (``_storage_Use_Count == 1``): tensors, views and anything
+    else sharing the storage keep it in use, which is the reference's rule that a
+    block returns when the last reference to the *storage* dies."""
+
+    __slots__ = ("device", "nbytes", "storage", "stream")
+
+    def __init__(self, storage: torch.UntypedStorage, nbytes: int, device: torch.device, stream: int) -> None:
+        self.storage, self.nbytes, self.device, self.stream = storage, nbytes, device, stream
+
+    def unused(self) -> bool:
+        return torch._C._storage_Use_Count(self.storage._cdata) == 1
+
+
+_MAX_FREE_BLOCKS = 64
 _max_bytes = 0
 _wrap_failed = False
 _limit_applied = False
+_lock = threading.Lock()
+_blocks: list[_Block] = []  # oldest first
+_hits = 0
+_misses = 0
 
 
 def _plain_dispatch() -> bool:
@@ -120,35 +147,76 @@ def _default_strides(sizes: tuple[int, ...]) -> tuple[int, ...]:
     return tuple(strides)
 
 
-def _allocate(sizes: tuple[int, ...], count: int, dtype: torch.dtype, device: torch.device) -> torch.Tensor | None:
-    nbytes = dtype.itemsize * count
-    pointer = ctypes.c_void_p()
-    hit = ctypes.c_int32()
-    if device.index is None:
-        device = torch.device("cuda", torch.cuda.current_device())
-    lib = native.module()
-    global _limit_applied
-    if not _limit_applied:  # the limit chosen at import, handed over once the library is loaded
-        _limit_applied = True
-        lib.b200_pool_set_limit(_max_bytes)
-    with torch.cuda.device(device):
-        code = lib.b200_pool_alloc(nbytes, native.stream_ptr(device), ctypes.byref(pointer), ctypes.byref(hit))
-    if code != 0 or not pointer.value:
-        return None  # torch's own attempt raises its error
-    rounded = -(-nbytes // _GRANULE) * _GRANULE
-    lease = _Lease(pointer.value, rounded, device)  # its __del__ returns the block, also on failure below
+def _settle_locked() -> None:
+    """Drop free blocks over the limits, oldest first (their memory goes back to the
+    library's pool, which applies the same limit before it frees device memory)."""
+    free = [b for b in _blocks if b.unused()]
+    free_bytes = sum(b.nbytes for b in free)
+    for block in free:
+        if free_bytes <= _max_bytes and len(free) <= _MAX_FREE_BLOCKS and block.nbytes <= _max_bytes:
+            break
+        _blocks.remove(block)
+        free_bytes -= block.nbytes
+        free = free[1:]
+
+
+def _wrap(pointer: int, rounded: int, device: torch.device) -> torch.UntypedStorage | None:
+    lease = _Lease(pointer, rounded, device)  # its __del__ returns the block, also on failure below
     try:
         flat = torch.as_tensor(lease, device=device)
         del lease  # the storage now owns the only reference
-        # Shaped in place on the pool's storage: a plain tensor, not a view of `flat`.
-        out = torch.empty(0, dtype=dtype, device=device)
-        out.set_(flat.untyped_storage(), 0, sizes, _default_strides(sizes))
+        return flat.untyped_storage()
     except (RuntimeError, TypeError, ValueError) as exc:
         global _wrap_failed
         if not _wrap_failed:
             _wrap_failed = True
-            warnings.warn(f"output pool: cannot wrap a device block as a tensor ({exc}); using torch.empty", stacklevel=3)
+            warnings.warn(f"output pool: cannot wrap a device block as a tensor ({exc}); using torch.empty", stacklevel=4)
         return None
+
+
+def _allocate(sizes: tuple[int, ...], count: int, dtype: torch.dtype, device: torch.device) -> torch.Tensor | None:
+    global _hits, _misses, _limit_applied
+    nbytes = dtype.itemsize * count
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    rounded = -(-nbytes // _GRANULE) * _GRANULE
+    stream = native.stream_ptr(device)
+    storage = None
+    strides = _default_strides(sizes)
+    with _lock:
+        # Newest first: most likely still in L2. Only blocks last used on this stream:
+        # stream order then protects the previous user's pending work.
+        for block in reversed(_blocks):
+            if block.nbytes == rounded and block.device == device and block.stream == stream and block.unused():
+                # The tensor is shaped onto the storage before the lock is given up:
+                # that reference is what makes the block "in use" for other threads.
+                out = torch.empty(0, dtype=dtype, device=device)
+                out.set_(block.storage, 0, sizes, strides)
+                _hits += 1
+                _blocks.remove(block)
+                _blocks.append(block)
+                return out
+        _misses += 1
+    if storage is None:
+        lib = native.module()
+        if not _limit_applied:  # the limit chosen at import, handed over once the library is loaded
+            _limit_applied = True
+            lib.b200_pool_set_limit(_max_bytes)
+        pointer = ctypes.c_void_p()
+        hit = ctypes.c_int32()
+        with native.on_device(device):
+            code = lib.b200_pool_alloc(nbytes, stream, ctypes.byref(pointer), ctypes.byref(hit))
+        if code != 0 or not pointer.value:
+            return None  # torch's own attempt raises its error
+        storage = _wrap(pointer.value, rounded, device)
+        if storage is None:
+            return None
+        # Shaped in place on the pool's storage: a plain tensor, not a view.
+        out = torch.empty(0, dtype=dtype, device=device)
+        out.set_(storage, 0, sizes, strides)
+        with _lock:
+            _blocks.append(_Block(storage, rounded, device, stream))
+            _settle_locked()
     return out
 
 
@@ -189,6 +257,8 @@ def set_output_pool(max_bytes: int) -> None:
     them. Tensors using a block are unaffected."""
     global _max_bytes, _limit_applied
     _max_bytes = max(0, int(max_bytes))
+    with _lock:
+        _settle_locked()
     try:
         native.module().b200_pool_set_limit(_max_bytes)
         _limit_applied = True
@@ -198,21 +268,27 @@ def set_output_pool(max_bytes: int) -> None:
 
 def release() -> None:
     """Free every free block now; tensors using a block are unaffected."""
+    with _lock:
+        for block in [b for b in _blocks if b.unused()]:
+            _blocks.remove(block)
     native.module().b200_pool_release()
 
 
 def output_pool_stats() -> dict[str, int]:
-    stats = native.PoolStats()
-    native.module().b200_pool_stats(ctypes.byref(stats))
-    return {
-        "hits": int(stats.hits),
-        "misses": int(stats.misses),
-        "free_blocks": int(stats.free_blocks),
-        "free_bytes": int(stats.free_bytes),
-        "max_bytes": _max_bytes,
-        "live_blocks": int(stats.live_blocks),
-        "live_bytes": int(stats.live_bytes),
-    }
+    with _lock:
+        _settle_locked()
+        free = [b for b in _blocks if b.unused()]
+        live = len(_blocks) - len(free)
+        live_bytes = sum(b.nbytes for b in _blocks) - sum(b.nbytes for b in free)
+        return {
+            "hits": _hits,
+            "misses": _misses,
+            "free_blocks": len(free),
+            "free_bytes": sum(b.nbytes for b in free),
+            "max_bytes": _max_bytes,
+            "live_blocks": live,
+            "live_bytes": live_bytes,
+        }
 
 
 def enabled() -> bool:

@@ -16,7 +16,7 @@ def _eltwise(kind: int, x: Tensor, param: float) -> Tensor:
     device = native.require_cuda(x)
     x = x.contiguous()
     out = output_pool.empty_like(x)
-    with torch.cuda.device(device):
+    with native.on_device(device):
         code = native.module().b200_eltwise(
             kind, native.dtype_code(x.dtype), x.data_ptr(), out.data_ptr(), x.numel(), float(param),
             native.stream_ptr(device),

@@ -69,13 +69,18 @@ def _round_up(value: int, block: int) -> int:
     return (value + block - 1) // block * block
 
 
+_SM_COUNTS: dict[int, int] = {}
+
+
 def _sm_count() -> int:
-    """SMs of the current device (148 when there is none to ask)."""
+    """SMs of the current device (148 when there is none to ask); asked once per device."""
     try:
         if torch.cuda.is_available():
-            count = int(native.module().b200_sm_count())
-            if count > 0:
-                return count
+            device = torch.cuda.current_device()
+            count = _SM_COUNTS.get(device)
+            if count is None:
+                count = _SM_COUNTS[device] = int(native.module().b200_sm_count()) or _DEFAULT_SMS
+            return count
     except (ImportError, OSError):
         pass
     return _DEFAULT_SMS
@@ -91,7 +96,7 @@ def _pack(kind: int, src: Tensor, rows_pad: int, cols_pad: int, shape: tuple[int
     src = src.contiguous()
     rows, cols = map(int, src.shape)
     out = output_pool.empty(shape, dtype=src.dtype, device=device)
-    with torch.cuda.device(device):
+    with native.on_device(device):
         code = native.module().b200_pack(
             kind, native.dtype_code(src.dtype), src.data_ptr(), rows, cols, cols, out.data_ptr(), rows_pad, cols_pad,
             panel, native.stream_ptr(device),
@@ -300,7 +305,7 @@ class GemmPlan:
             if need:
                 workspace = output_pool.empty((need,), dtype=torch.uint8, device=self.device)
                 desc.workspace, desc.workspace_bytes = workspace.data_ptr(), need
-        with torch.cuda.device(self.device):
+        with native.on_device(self.device):
             code = lib.b200_gemm(ctypes.byref(desc), native.stream_ptr(self.device))
         native.check("b200_gemm", code)
         self.launches += 1
@@ -670,7 +675,7 @@ def unpack_b_to_nk(b4: Tensor) -> Tensor:
     else:
         raise ValueError(f"unpack_b_to_nk() expects a VNNI-packed tensor, got {tuple(b4.shape)}")
     out = output_pool.empty((n_pad, k_pad), dtype=b4.dtype, device=device)
-    with torch.cuda.device(device):
+    with native.on_device(device):
         code = native.module().b200_pack(
             kind, native.BF16, b4.data_ptr(), 0, 0, 0, out.data_ptr(), n_pad, k_pad, panel, native.stream_ptr(device)
         )

@@ -59,7 +59,7 @@ def softmax(x: Tensor, in_place: bool = False) -> Tensor:
     m, n = map(int, x.shape)
     x = x.contiguous()
     out = _out_for(x, in_place)
-    with torch.cuda.device(device):
+    with native.on_device(device):
         code = native.module().b200_softmax(
             native.dtype_code(x.dtype), x.data_ptr(), out.data_ptr(), m, n, n, native.stream_ptr(device)
         )
@@ -133,7 +133,7 @@ def group_norm(
 def _group_norm_call(x, m, groups, c, weight, bias, extra, extra_op, act, alpha, eps, param_dtype, device, out):
     if out is None:
         out = output_pool.empty_like(x)
-    with torch.cuda.device(device):
+    with native.on_device(device):
         code = native.module().b200_group_norm(
             native.dtype_code(x.dtype),
             native.dtype_code(param_dtype),
@@ -178,7 +178,7 @@ def rms_norm(x: Tensor, weight: Tensor | None = None, eps: float = 1e-5, in_plac
         weight = weight.to(param_dtype).contiguous()
     x = x.contiguous()
     out = _out_for(x, in_place)
-    with torch.cuda.device(device):
+    with native.on_device(device):
         code = native.module().b200_rms_norm(
             native.dtype_code(x.dtype),
             native.dtype_code(param_dtype),

@@ -45,7 +45,7 @@ def _row_reduce(kind: int, x: Tensor, v: Tensor | None, epilogue: Callable[[Tens
     out = output_pool.empty((m, 1), dtype=out_dtype, device=device)
     if v is not None and kind == native.REDUCE_MATVEC and src.dtype != v.dtype:
         v = v.to(src.dtype)
-    with torch.cuda.device(device):
+    with native.on_device(device):
         code = native.module().b200_row_reduce(
             kind, native.dtype_code(src.dtype), src.data_ptr(), native.ptr(v), out.data_ptr(), m, n, n, act, alpha,
             native.stream_ptr(device),
@@ -103,7 +103,7 @@ def column_sum(x: Tensor) -> Tensor:
     out = output_pool.empty((n,), dtype=torch.float32, device=device)
     need = int(lib.b200_column_sum_workspace_bytes(m, n))
     workspace = output_pool.empty((need,), dtype=torch.uint8, device=device) if need else None
-    with torch.cuda.device(device):
+    with native.on_device(device):
         code = lib.b200_column_sum(
             native.dtype_code(x.dtype), x.data_ptr(), out.data_ptr(), m, n, n, native.ptr(workspace), need,
             native.stream_ptr(device),
