@@ -20,6 +20,7 @@ namespace b200 {
 int umma_supports(const b200_gemm_desc& d);
 int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* partials, cudaStream_t stream);
 int explain_gemm_umma(const b200_gemm_desc& d, char* buf, size_t len);
+int run_wait_timeout_selftest(unsigned long long budget_ns, cudaStream_t stream);
 int run_gemm_simt(const b200_gemm_desc& d, const GemmOperand& a, const GemmOperand& b, const GemmEpilogue& epi,
                   int splits, float* workspace, cudaStream_t stream);
 
@@ -315,4 +316,10 @@ extern "C" int b200_gemm_explain(const b200_gemm_desc* desc, char* buf, size_t b
                                        : "",
            inner);
   return 0;
+}
+
+extern "C" int b200_selftest_wait_timeout(uint64_t budget_ns, void* stream) {
+  if (!enabled()) return refuse(B200_E_DISABLED);
+  if (budget_ns == 0 || budget_ns > 1000000000ull) return refuse(B200_E_ARG);  // at most one second
+  return run_wait_timeout_selftest(budget_ns, static_cast<cudaStream_t>(stream));
 }

@@ -46,7 +46,7 @@ constexpr uint32_t kAccStride = 256;  // TMEM columns between the two accumulato
 constexpr unsigned long long kWaitBudgetNs = 2000000000ull;
 
 // Status bits (also reported through b200_read_kernel_status).
-constexpr int kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueWait = 4, kErrDrainWait = 8;
+constexpr int kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueWait = 4, kErrDrainWait = 8, kErrSelfTest = 16;
 
 struct UmmaParams {
   int32_t m, n, k, batch;
@@ -106,14 +106,14 @@ __device__ __forceinline__ unsigned long long global_ns() {
 // Waits for the phase of `parity` to complete. Gives up when the CTA aborted or
 // after kWaitBudgetNs; returns false then (and raises the abort with `code`).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
-                                          int code) {
+                                          int code, unsigned long long budget_ns = kWaitBudgetNs) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long start = global_ns();
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((spin & 63u) == 0) {
       if (*abort_flag) return false;
-      if (global_ns() - start > kWaitBudgetNs) {
+      if (global_ns() - start > budget_ns) {
         *abort_flag = 1;
         if (status) atomicOr(status, code);
         return false;
@@ -629,6 +629,20 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 }
 
+// Waits on a barrier nothing ever arrives on: the wait must run out after
+// `budget_ns`, leave kErrSelfTest in the status word and return normally.
+__global__ void wait_timeout_selftest_kernel(unsigned long long budget_ns, int32_t* status) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  mbar_wait(smem_u32(&bar), 0, &abort_flag, status, kErrSelfTest, budget_ns);
+}
+
 // --------------------------------------------------------------------------- host
 
 using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -853,6 +867,14 @@ int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* parti
   if (rc != 0) return finish(rc);
   return launch_splitk_reduce(partials, plan.psplits, d.batch, d.m, d.n, d.c, d.out_dtype == B200_BF16, d.ldc,
                               d.stride_c, epi, stream);
+}
+
+int run_wait_timeout_selftest(unsigned long long budget_ns, cudaStream_t stream) {
+  if (device_info().sm_count == 0) return refuse(B200_E_DEVICE);
+  int32_t* status = kernel_status_word();
+  if (!status) return refuse(B200_E_DEVICE);
+  wait_timeout_selftest_kernel<<<1, 32, 0, stream>>>(budget_ns, status);
+  return launched();
 }
 
 int explain_gemm_umma(const b200_gemm_desc& d, char* buf, size_t len) {

@@ -167,6 +167,7 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "b200_get_counters": (c_int, [ctypes.POINTER(Counters)]),
     "b200_reset_counters": (c_int, []),
     "b200_read_kernel_status": (c_int, [c_void_p, ctypes.POINTER(c_int32)]),
+    "b200_selftest_wait_timeout": (c_int, [c_uint64, c_void_p]),
     "b200_strerror": (c_char_p, [c_int]),
     "b200_abi_version": (c_int, []),
     "b200_set_enabled": (c_int, [c_int]),

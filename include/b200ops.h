@@ -260,6 +260,15 @@ int b200_reset_counters(void);
  * (0 = none). Reading it synchronises the given stream. */
 int b200_read_kernel_status(void* stream, int32_t* out_status);
 
+/* Self-test of the failure path of the kernels' bounded waits (no counterpart in
+ * the reference, whose failure handling is host-side: compile time-outs,
+ * _compiler/execution.py:611-647). Launches one warp that waits, for at most
+ * `budget_ns` (1..1e9), on a barrier nothing arrives on. The wait must give up,
+ * OR the bit 16 into the kernel status word and return normally: afterwards
+ * b200_read_kernel_status reports 16 and the context keeps working. Nothing
+ * faults, traps or hangs. */
+int b200_selftest_wait_timeout(uint64_t budget_ns, void* stream);
+
 const char* b200_strerror(int code);
 int b200_abi_version(void);
 /* 0 makes every compute entry point refuse with B200_E_DISABLED (set_native_call(False)). */

@@ -229,3 +229,25 @@ def test_single_cta_and_cta_pair_tiles_agree(ops, shape, trans_a: bool, trans_b:
     out = plan.run(da, db, dbias)
     checks.assert_parity(BF16, out.cpu(), ref.matmul(a, b, bias=bias, epilogue=torch.relu), text)
     assert torch.equal(out, plan.run(da, db, dbias))
+
+
+def test_bounded_wait_gives_up_and_reports() -> None:
+    """Failure detection without a fault: a wait that nothing satisfies runs out after
+    its budget, leaves a code in the device status word, and the context stays usable."""
+    import time
+
+    from helion_mlir_backend import native
+
+    lib = native.module()
+    torch.cuda.synchronize()
+    assert native.kernel_status() == 0
+    stream = native.stream_ptr(torch.device("cuda", 0))
+    t0 = time.perf_counter()
+    assert lib.b200_selftest_wait_timeout(2_000_000, stream) == 0  # 2 ms
+    status = native.kernel_status()  # synchronises
+    elapsed = time.perf_counter() - t0
+    assert status == 16 and elapsed < 1.0
+    assert native.kernel_status() == 0  # reading clears the word
+    assert lib.b200_selftest_wait_timeout(0, stream) == 7
+    x = torch.randn(64, 64, device="cuda")
+    assert torch.allclose(torch.softmax(x, -1), __import__("helion_mlir_utils").softmax(x), atol=1e-6)
