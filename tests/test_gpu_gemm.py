@@ -251,3 +251,24 @@ def test_bounded_wait_gives_up_and_reports() -> None:
     assert lib.b200_selftest_wait_timeout(0, stream) == 7
     x = torch.randn(64, 64, device="cuda")
     assert torch.allclose(torch.softmax(x, -1), __import__("helion_mlir_utils").softmax(x), atol=1e-6)
+
+
+def test_seeded_shape_sweep(ops) -> None:
+    """Forty seeded shapes (multiples of 8, so that the tensor-core path applies) in
+    random orientations, with and without a fused epilogue, against the oracle."""
+    import random
+
+    rng = random.Random(2024)
+    gen = torch.Generator().manual_seed(2024)
+    for case in range(40):
+        m, n, k = (8 * rng.randint(1, 90) for _ in range(3))
+        trans_a, trans_b = rng.random() < 0.5, rng.random() < 0.5
+        a, b = rand(gen, m, k), rand(gen, k, n, scale=0.5)
+        bias = rand(gen, n) if rng.random() < 0.5 else None
+        fn = rng.choice([ops.identity_epilogue, torch.relu, F.gelu])
+        a_in = a.T.contiguous() if trans_a else a
+        b_in = b.T.contiguous() if trans_b else b
+        da, db = cuda(a_in, b_in)
+        out = ops.matmul(da, db, trans_a=trans_a, trans_b=trans_b, bias=None if bias is None else cuda(bias), epilogue=fn)
+        expect = ref.matmul(a, b, bias=bias, epilogue=fn)
+        checks.assert_parity(BF16, out.cpu(), expect, f"case {case}: {(m, n, k)} ta={trans_a} tb={trans_b} {fn.__name__}")
