@@ -40,10 +40,6 @@ def register_body(body: Callable[..., object], factory: Callable[[tuple[int, ...
 
 def recognise(fn: Callable[..., object], config: object | None = None) -> Callable[..., object] | None:
     """The native callable for kernel body ``fn`` under ``config``, or ``None``."""
-    code = getattr(fn, "__code__", None)
-    factory = _RECOGNISED.get(code)
-    if factory is None:
-        return None
     block_sizes = None
     if config is not None:
         values = getattr(config, "config", config)
@@ -51,7 +47,14 @@ def recognise(fn: Callable[..., object], config: object | None = None) -> Callab
             block_sizes = tuple(int(v) for v in values.get("block_sizes", ()))  # type: ignore[union-attr]
         except AttributeError:
             block_sizes = None
-    return factory(block_sizes)
+    code = getattr(fn, "__code__", None)
+    factory = _RECOGNISED.get(code)
+    if factory is not None:
+        return factory(block_sizes)
+    # The bodies of the reference's operator set, known by name and parameter list.
+    from .bodies import adapter_for
+
+    return adapter_for(fn, block_sizes)
 
 
 def make_backend_class(base: type) -> type:
