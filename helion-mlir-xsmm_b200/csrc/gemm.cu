@@ -178,7 +178,7 @@ b200_gemm_desc split_desc(const b200_gemm_desc& d, void* a_wide, void* b_wide) {
   u.lda = d.a_layout == B200_LAYOUT_ROW ? u.k : d.m;  // [M, 6K] or [6K, M]
   u.ldb = d.b_layout == B200_LAYOUT_COL ? u.k : d.n;  // [N, 6K] or [6K, N]
   // chunks of the widened K are added in f32 by the epilogue (needs an f32 result)
-  u.split_k = d.out_dtype == B200_F32 ? static_cast<int32_t>(ceil_div(u.k, kSplitChunkK)) : 0;
+  u.split_k = static_cast<int32_t>(ceil_div(u.k, kSplitChunkK));
   if (u.split_k < 2) u.split_k = 0;
   u.workspace = nullptr;
   u.workspace_bytes = 0;
@@ -268,7 +268,6 @@ extern "C" int b200_gemm(const b200_gemm_desc* desc, void* stream) {
     return run_gemm_umma(split_desc(d, wide, wide + r.split_a_bytes), r.epi, nullptr, s);
   }
 
-  if (d.split_k > 1 && !partials && d.out_dtype != B200_F32) return refuse(B200_E_WORKSPACE);
   if (path == kPathUmmaUnpack) {
     if (r.unpack_a_bytes) {
       const int rc =

@@ -236,6 +236,18 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_field, uint32_t hi) {
   const uint32_t lo = ((smem_addr & 0x3FFFFu) >> 4) | (lbo_field << 16);
@@ -363,6 +375,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const bool leader = rank == 0;
   const int64_t first_work = blockIdx.x / CG, work_stride = gridDim.x / CG;
   constexpr int kTileRows = kBlockM * CG;
+  const bool serial = p.splits > 1;
   const int b_rows = p.block_n / CG;  // columns of the B tile this CTA stages
 
   if (threadIdx.x == 0) {
@@ -469,7 +482,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool ok = true;
       for (int64_t work = first_work; work < total_work && ok; work += work_stride) {
         for (int s = 0; s < p.splits && ok; ++s, ++phase) {
-          const uint32_t acc = phase & 1u, acc_round = phase >> 1;
+          // Without splits the two TMEM halves double-buffer the accumulator; with serial
+          // splits the accumulator is half 0 and half 1 holds the running sum of the splits.
+          const uint32_t acc = serial ? 0u : (phase & 1u), acc_round = serial ? phase : (phase >> 1);
           ok = mbar_wait(smem_u32(&bars->acc_empty[acc]), (acc_round & 1u) ^ 1u, abort_flag, p.status, kErrMmaWait);
           if (!ok) break;
           tc_fence_after();
@@ -516,40 +531,54 @@ __global__ void __launch_bounds__(kThreads, 1)
                         row * p.ldc) *
                            (p.out_bf16 ? 2 : 4);
       for (int s = 0; s < p.splits && ok; ++s, ++phase) {
-        const uint32_t acc = phase & 1u, acc_round = phase >> 1;
+        const uint32_t acc = serial ? 0u : (phase & 1u), acc_round = serial ? phase : (phase >> 1);
         ok = mbar_wait(smem_u32(&bars->acc_full[acc]), acc_round & 1u, abort_flag, p.status, kErrEpilogueWait);
         ok = __all_sync(0xffffffffu, ok) != 0;
         if (!ok) break;
         tc_fence_after();
         const bool last = s == p.splits - 1;
-        for (int c0 = half * half_cols; c0 < (half + 1) * half_cols; c0 += 32) {
+        const int c_begin = half * half_cols, c_end = (half + 1) * half_cols;
+        for (int c0 = c_begin; c0 < c_end; c0 += 32) {
           uint32_t raw[32];
           tmem_ld_32x32(tmem_base + lane_base + acc * kAccStride + c0, raw);
-          tmem_ld_wait();
+          float v[32];
+          if (serial) {
+            // Ordered split-K: the running sum of the splits lives in the other TMEM
+            // half, so partial sums never leave the SM. s = 0 starts it, later splits
+            // add to it in ascending order, the last one goes on to the epilogue.
+            const uint32_t sum_addr = tmem_base + lane_base + kAccStride + c0;
+            uint32_t prev[32];
+            if (s > 0) tmem_ld_32x32(sum_addr, prev);
+            tmem_ld_wait();
+            // This warp's share of the accumulator is in registers once its last chunk
+            // is loaded: the MMA warp may overwrite it with the next split.
+            if (c0 + 32 >= c_end) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) {
+                if (CG == 2)
+                  mbar_arrive_leader(smem_u32(&bars->acc_empty[acc]));
+                else
+                  mbar_arrive(smem_u32(&bars->acc_empty[acc]));
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]) + (s > 0 ? __uint_as_float(prev[j]) : 0.f);
+            if (!last) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) raw[j] = __float_as_uint(v[j]);
+              tmem_st_32x32(sum_addr, raw);
+              tmem_st_wait();
+              continue;
+            }
+          } else {
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+          }
           const int64_t col0 = static_cast<int64_t>(t.n0) + c0;
           if (!row_ok || col0 >= p.n) continue;
-          float v[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
           const bool full_chunk = col0 + 32 <= p.n;
-          if (s > 0) {
-            // Serial split-K: partial sums live in C (f32) and are added in split order.
-            const float* prev = reinterpret_cast<const float*>(c_row) + col0;
-            if (full_chunk && p.vec_store) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const float4 q = *reinterpret_cast<const float4*>(prev + 4 * j);
-                v[4 * j] += q.x;
-                v[4 * j + 1] += q.y;
-                v[4 * j + 2] += q.z;
-                v[4 * j + 3] += q.w;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.n) v[j] += prev[j];
-            }
-          }
           if (last) {
             const bool vec_fast = full_chunk && p.vec_params;
             if (p.epi.bias) {
@@ -602,14 +631,17 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
           }
         }
-        // This warp has read the whole accumulator: hand it back to the MMA warp.
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) {
-          if (CG == 2)
-            mbar_arrive_leader(smem_u32(&bars->acc_empty[acc]));
-          else
-            mbar_arrive(smem_u32(&bars->acc_empty[acc]));
+        // This warp has read the whole accumulator: hand it back to the MMA warp
+        // (with serial splits that happened right after the last chunk was loaded).
+        if (!serial) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+            if (CG == 2)
+              mbar_arrive_leader(smem_u32(&bars->acc_empty[acc]));
+            else
+              mbar_arrive(smem_u32(&bars->acc_empty[acc]));
+          }
         }
       }
     }

@@ -849,9 +849,9 @@ def bmm(a: Tensor, b: Tensor, split_k: int | None = None, out_dtype: torch.dtype
     a, b = a.contiguous(), b.contiguous()
     final = a.dtype if out_dtype is None else out_dtype
     splits = 0 if split_k is None or split_k <= 1 else int(split_k)
-    # In-kernel ordered splits keep partial sums in the f32 output; other output
-    # types take the partial-sum workspace.
-    parallel = splits > 1 and final != torch.float32
+    # The tensor-core kernel sums the ordered splits on chip; the FFMA kernel keeps
+    # them in an f32 output and takes the partial-sum workspace for other types.
+    parallel = splits > 1 and a.dtype != torch.bfloat16 and final != torch.float32
     key = ("bmm", batch, m, n, k, a.dtype, device, final, splits, _tensor_key(b))
 
     def build() -> GemmPlan:

@@ -112,8 +112,9 @@ def test_bmm_and_split_k(ops) -> None:
     assert serial.dtype == F32
     assert checks.rel_frobenius(serial.cpu(), ref.bmm(a, b, split_k=4, out_dtype=F32)) < 1e-5
     assert torch.equal(serial, ops.bmm(da, db, split_k=4, out_dtype=F32))  # ordered: same bits every run
-    rounded = ops.bmm(da, db, split_k=4)  # bf16 result: partial-sum workspace + ordered reduction
+    rounded = ops.bmm(da, db, split_k=4)  # bf16 result of the same on-chip ordered sum
     checks.assert_parity(BF16, rounded.cpu(), ref.bmm(a, b, split_k=4), "bmm split bf16")
+    assert torch.equal(rounded, serial.to(BF16))
     # parallel split-K chosen automatically: few tiles, deep K
     a2, b2 = rand(gen, 128, 8192), rand(gen, 8192, 128)
     text = explain(ops, *cuda(a2, b2))
