@@ -175,15 +175,14 @@ class LinearGelu(Workload):
         self.xs = _rotating(self.SETS, lambda i: data["x"].roll(i, 0).to(device))
         self.x_pinned = data["x"].pin_memory()
         self.y_pinned = torch.empty(self.M, self.N, dtype=torch.bfloat16).pin_memory()
-        self.x_stage = torch.empty_like(self.xs[0])
 
     def step(self, index: int) -> torch.Tensor:
         return self.ops.matmul(self.xs[index % self.SETS], self.w, trans_b=True, bias=self.b, epilogue=F.gelu)
 
     def e2e_step(self, index: int) -> tuple[int, int]:
-        self.x_stage.copy_(self.x_pinned, non_blocking=True)
-        y = self.ops.matmul(self.x_stage, self.w, trans_b=True, bias=self.b, epilogue=F.gelu)
-        self.y_pinned.copy_(y, non_blocking=True)
+        # Host rows in, host rows out (b200_gemm_host_rows): copy-in, GEMM and copy-out
+        # of neighbouring row chunks overlap on three streams.
+        self.ops.matmul_host(self.x_pinned, self.w, self.y_pinned, trans_b=True, bias=self.b, epilogue=F.gelu)
         return self.x_pinned.numel() * 2, self.y_pinned.numel() * 2
 
     def work_per_step(self) -> float:
@@ -230,7 +229,6 @@ class RowNorms(Workload):
         self.g16, self.b16 = self.g32.bfloat16(), self.b32.bfloat16()
         self.x_pinned = data["x"].pin_memory()
         self.y_pinned = torch.empty(self.M, self.N).pin_memory()
-        self.x_stage = torch.empty_like(self.x32)
 
     def step(self, index: int) -> torch.Tensor:
         ops = self.ops
@@ -242,9 +240,7 @@ class RowNorms(Workload):
         return ops.rms_norm(self.x16, self.g16, 1e-5)
 
     def e2e_step(self, index: int) -> tuple[int, int]:
-        self.x_stage.copy_(self.x_pinned, non_blocking=True)
-        y = self.ops.softmax(self.x_stage)
-        self.y_pinned.copy_(y, non_blocking=True)
+        self.ops.stream_rows(self.ops.softmax, self.x_pinned, self.y_pinned)
         return self.x_pinned.numel() * 4, self.y_pinned.numel() * 4
 
     def work_per_step(self) -> float:

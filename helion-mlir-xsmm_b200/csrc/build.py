@@ -29,6 +29,7 @@ SOURCES = [
     "gemm.cu",
     "gemm_simt.cu",
     "gemm_umma.cu",
+    "host_rows.cu",
 ]
 HEADERS = ["common.cuh", "gemm_common.cuh", "../../include/b200ops.h"]
 FLAGS = [

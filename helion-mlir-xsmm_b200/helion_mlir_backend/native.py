@@ -125,6 +125,8 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "b200_gemm": (c_int, [ctypes.POINTER(GemmDesc), c_void_p]),
     "b200_gemm_explain": (c_int, [ctypes.POINTER(GemmDesc), c_char_p, c_size_t]),
     "b200_gemm_workspace_bytes": (c_size_t, [ctypes.POINTER(GemmDesc)]),
+    "b200_gemm_host_rows": (c_int, [ctypes.POINTER(GemmDesc), c_void_p, c_void_p, c_int64, c_void_p]),
+    "b200_host_rows_release": (c_int, []),
     "b200_pack": (
         c_int,
         [c_int32, c_int32, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int32, c_void_p],

@@ -11,6 +11,7 @@ from __future__ import annotations
 from .elementwise import leaky_relu
 from .elementwise import relu
 from .elementwise import scalar_mul
+from .host_io import stream_rows
 from .epilogues import gelu_tanh
 from .epilogues import leaky_relu_epilogue
 from .kernels import per_config
@@ -24,6 +25,7 @@ from .matmul import bmm
 from .matmul import identity_epilogue
 from .matmul import matmul
 from .matmul import matmul_blocked
+from .matmul import matmul_host
 from .matmul import matmul_prepacked_b
 from .matmul import matmul_prepacked_b_affine
 from .matmul import pack_a_blocked
@@ -77,6 +79,7 @@ __all__ = [
     "linear_affine",
     "matmul",
     "matmul_blocked",
+    "matmul_host",
     "matmul_prepacked_b",
     "matmul_prepacked_b_affine",
     "matvec",
@@ -100,6 +103,7 @@ __all__ = [
     "shard_bounds",
     "shard_rows",
     "softmax",
+    "stream_rows",
     "supports",
     "supports_matvec",
     "tall_output_tiles",

@@ -313,6 +313,34 @@ class GemmPlan:
             out = self.post(out).to(self.final_dtype)
         return out
 
+    def run_host(self, a_host: Tensor, b: Tensor, bias: Tensor | None, scale: Tensor | None, shift: Tensor | None,
+                 out_host: Tensor, chunk_rows: int) -> Tensor:
+        """The same GEMM with ``a_host`` read from and ``out_host`` written to host
+        memory, row chunks streamed through the library's staging ring."""
+        desc = self.desc
+        vec = self.vec_dtype
+        bias = None if bias is None else bias.to(vec)
+        scale = None if scale is None else scale.to(vec)
+        shift = None if shift is None else shift.to(vec)
+        # Stand-ins for the staged chunks (the library substitutes its ring): only
+        # compared with the other operands' address ranges, never dereferenced.
+        desc.a, desc.c, desc.b = 1 << 45, 1 << 46, b.data_ptr()
+        desc.bias, desc.scale, desc.shift = native.ptr(bias), native.ptr(scale), native.ptr(shift)
+        lib = native.module()
+        workspace = None
+        desc.workspace, desc.workspace_bytes = None, 0
+        if self._wants_workspace:
+            need = int(lib.b200_gemm_workspace_bytes(ctypes.byref(desc)))
+            if need:
+                workspace = output_pool.empty((need,), dtype=torch.uint8, device=self.device)
+                desc.workspace, desc.workspace_bytes = workspace.data_ptr(), need
+        with native.on_device(self.device):
+            code = lib.b200_gemm_host_rows(ctypes.byref(desc), a_host.data_ptr(), out_host.data_ptr(), chunk_rows,
+                                           native.stream_ptr(self.device))
+        native.check("b200_gemm_host_rows", code)
+        self.launches += 1
+        return out_host
+
     def explain(self, a: Tensor, b: Tensor) -> CallExplanation:
         desc = native.GemmDesc.from_buffer_copy(self.desc)  # the plan's own descriptor stays as planned
         desc.a, desc.b = a.data_ptr(), b.data_ptr()
@@ -361,6 +389,7 @@ def _plan_gemm(
     out_shape: tuple[int, ...] | None = None,
     ldc: int | None = None,
     force_kernel: int = 0,
+    device: torch.device | None = None,
 ) -> GemmPlan:
     fused = epilogues.resolve(epilogue)
     final_dtype = a.dtype if out_dtype is None else out_dtype
@@ -385,8 +414,8 @@ def _plan_gemm(
         desc.tile_m, desc.tile_n, desc.tile_k = hint[0], hint[1], hint[2]
     desc.force_kernel = force_kernel
     shape = (m, n) if out_shape is None else out_shape
-    return GemmPlan(desc, a.device, shape, kernel_out, None if fused is not None else epilogue, final_dtype,
-                    vec_dtype, parallel_split)
+    return GemmPlan(desc, a.device if device is None else device, shape, kernel_out,
+                    None if fused is not None else epilogue, final_dtype, vec_dtype, parallel_split)
 
 
 # LRU of launch plans keyed by problem, like the reference's cache of bound
@@ -497,6 +526,66 @@ def matmul(
     plan = _matmul_plan(a, b, trans_a, trans_b, bias, epilogue, block_sizes, scale, shift, out_dtype, split_k)
     trace(f"matmul {tuple(a.shape)} x {tuple(b.shape)}")
     return plan.run(a, b, bias, scale, shift)
+
+
+def matmul_host(
+    a_host: Tensor,
+    b: Tensor,
+    out_host: Tensor | None = None,
+    trans_b: bool = False,
+    bias: Tensor | None = None,
+    epilogue: Callable[[Tensor], Tensor] = identity_epilogue,
+    scale: Tensor | None = None,
+    shift: Tensor | None = None,
+    out_dtype: torch.dtype | None = None,
+    chunk_rows: int | None = None,
+) -> Tensor:
+    """:func:`matmul` for activations in host memory (an extension): ``a_host``
+    ``[M, K]`` and the result ``[M, N]`` live in pinned host memory, ``b`` and the
+    epilogue vectors on the device. Row chunks are copied in, multiplied and copied
+    out on three streams at once, so a call costs about the larger of the two PCIe
+    transfers. Returns ``out_host`` (allocated pinned when not given) with
+    everything enqueued: synchronise the current stream before reading it. The
+    epilogue must be one the kernel fuses (see ``epilogues.resolve``)."""
+    if a_host.is_cuda or not b.is_cuda:
+        raise ValueError("matmul_host() takes a host a_host and a device b")
+    if a_host.dim() != 2 or b.dim() != 2 or a_host.dtype != b.dtype or a_host.dtype not in _SUPPORTED_DTYPES:
+        raise ValueError(f"matmul_host() needs 2-D bf16/f32 operands of one dtype, got {tuple(a_host.shape)} "
+                         f"{a_host.dtype} and {tuple(b.shape)} {b.dtype}")
+    m, k = map(int, a_host.shape)
+    n = int(b.shape[0]) if trans_b else int(b.shape[1])
+    if int(b.shape[1] if trans_b else b.shape[0]) != k:
+        raise ValueError(f"contracted sizes differ: {tuple(a_host.shape)} x {tuple(b.shape)} (trans_b={trans_b})")
+    if epilogues.resolve(epilogue) is None:
+        raise ValueError("matmul_host() needs an epilogue the kernel fuses; apply others to the host result")
+    final = a_host.dtype if out_dtype is None else out_dtype
+    if out_host is None:
+        out_host = torch.empty((m, n), dtype=final, pin_memory=True)
+    if out_host.is_cuda or tuple(out_host.shape) != (m, n) or out_host.dtype != final or not out_host.is_contiguous():
+        raise ValueError(f"out_host must be a contiguous host [{m}, {n}] {final} tensor")
+    if not a_host.is_contiguous():
+        raise ValueError("a_host must be contiguous")
+    device = b.device
+    b = b.contiguous()
+    if bias is not None and (bias.dim() != 1 or int(bias.shape[0]) != n):
+        raise ValueError(f"bias must have shape ({n},), got {tuple(bias.shape)}")
+    bias = None if bias is None else bias.to(device=device).contiguous()
+    scale, shift = _affine_vector(scale, n, b), _affine_vector(shift, n, b)
+    if m == 0:
+        return out_host
+    key = ("matmul_host", m, n, k, a_host.dtype, device, trans_b, _tensor_key(b), _tensor_key(bias),
+           _tensor_key(scale), _tensor_key(shift), final, epilogue)
+
+    def build() -> GemmPlan:
+        return _plan_gemm(
+            a=a_host, m=m, n=n, k=k, a_layout=native.LAYOUT_ROW,
+            b_layout=native.LAYOUT_COL if trans_b else native.LAYOUT_ROW, lda=k, ldb=int(b.shape[1]),
+            bias=bias, scale=scale, shift=shift, epilogue=epilogue, out_dtype=final, device=device,
+        )
+
+    trace(f"matmul_host {tuple(a_host.shape)} x {tuple(b.shape)}")
+    return _cached_plan(key, build).run_host(a_host, b, bias, scale, shift, out_host,
+                                             0 if chunk_rows is None else int(chunk_rows))
 
 
 def explain_matmul(a: Tensor, b: Tensor, **kwargs: object) -> CallExplanation:

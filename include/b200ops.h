@@ -129,6 +129,26 @@ int b200_gemm_explain(const b200_gemm_desc* desc, char* buf, size_t buf_len);
 /* Bytes of workspace b200_gemm needs for the parallel split-K form of `desc`. */
 size_t b200_gemm_workspace_bytes(const b200_gemm_desc* desc);
 
+/* b200_gemm for activations and results that live in host memory (the reference's
+ * operators take host tensors: matmul.py:1384-1432 `matmul`, linear.py `linear`;
+ * here the weights B and the epilogue vectors stay on the device). `desc` as for
+ * b200_gemm except that desc->a and desc->c are ignored: A is read from `a_host`
+ * (row-major, lda elements per row, batch 1) and C written to `c_host` (ldc
+ * elements per row). The rows move in chunks of `chunk_rows` (<= 0: about 16 MiB of
+ * A) through a library-owned ring of device staging buffers on two copy streams
+ * while the GEMM of each chunk runs on `stream`; copy-in, GEMM and copy-out of
+ * neighbouring chunks overlap, and so do back-to-back calls. Host memory should
+ * be pinned (cudaHostAlloc / cudaHostRegister): pageable memory works but copies
+ * synchronously. On return everything is enqueued; `stream` waits for the last
+ * copy-out, so synchronising `stream` makes `c_host` readable. `a_host` must hold
+ * its data when the call is made and stay unchanged until then. The first call on
+ * a device creates the streams and allocates the ring (cudaMalloc); a later call
+ * that needs a larger ring synchronises and reallocates. */
+int b200_gemm_host_rows(const b200_gemm_desc* desc, const void* a_host, void* c_host, int64_t chunk_rows,
+                        void* stream);
+/* Waits for the copy streams of the current device and frees its staging ring. */
+int b200_host_rows_release(void);
+
 /* Layout conversions (bit-exact copies with zero fill). `kind`: */
 enum {
   B200_PACK_PAD_2D = 0,         /* [r,c] -> [rows_pad, cols_pad]                       matmul.py:78-89 */
