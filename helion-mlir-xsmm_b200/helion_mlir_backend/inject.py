@@ -54,7 +54,14 @@ def recognise(fn: Callable[..., object], config: object | None = None) -> Callab
     # The bodies of the reference's operator set, known by name and parameter list.
     from .bodies import adapter_for
 
-    return adapter_for(fn, block_sizes)
+    adapter = adapter_for(fn, block_sizes)
+    if adapter is not None:
+        return adapter
+    # Any other body that is a plain tiled GEMM with an affine + activation store.
+    from .structure import gemm_adapter, gemm_body
+
+    body = gemm_body(fn)
+    return None if body is None else gemm_adapter(body, block_sizes)
 
 
 def make_backend_class(base: type) -> type:

@@ -58,6 +58,7 @@ from .sharding import gather_rows
 from .sharding import row_sharded
 from .sharding import shard_bounds
 from .sharding import shard_rows
+from .tuning import tune_matmul
 
 __all__ = [
     "CACHE_PREPACKED_WEIGHTS_ENV",
@@ -104,6 +105,7 @@ __all__ = [
     "shard_rows",
     "softmax",
     "stream_rows",
+    "tune_matmul",
     "supports",
     "supports_matvec",
     "tall_output_tiles",

@@ -36,6 +36,7 @@ from helion_mlir_backend.call_trace import CallExplanation
 from helion_mlir_backend.call_trace import trace
 
 from . import epilogues
+from . import tuning
 from .epilogues import identity_epilogue
 
 if TYPE_CHECKING:
@@ -452,18 +453,30 @@ def _matmul_plan(
     shift: Tensor | None,
     out_dtype: torch.dtype | None,
     split_k: int | None,
+    choice: tuning.Choice | None = None,
 ) -> GemmPlan:
     m = int(a.shape[1]) if trans_a else int(a.shape[0])
     n = int(b.shape[0]) if trans_b else int(b.shape[1])
     k = int(a.shape[0]) if trans_a else int(a.shape[1])
     explicit_split = split_k is not None and split_k > 1
+    plain = bias is None and scale is None and shift is None and epilogue is identity_epilogue
+    # A measured choice for this problem on this hardware overrules the heuristics,
+    # unless the caller fixed the tiles or the split.
+    if choice is None and block_sizes is None and split_k is None and a.dtype == torch.bfloat16:
+        choice = tuning.lookup(tune_key(a.dtype, m, n, k, trans_a, trans_b, bias is not None, epilogue), a.device)
+    force_kernel = 0
+    if choice is not None:
+        if choice.tile_n:
+            block_sizes = (_TILE_M, choice.tile_n, _TILE_K)
+        force_kernel = choice.force_kernel()
+        if choice.split_k > 1 and plain and split_k is None:
+            split_k = choice.split_k
     if split_k is None:
-        plain = bias is None and scale is None and shift is None and epilogue is identity_epilogue
         split_k = _split_k(m, n, k) if plain else 0
     key = (
         "matmul", m, n, k, a.dtype, a.device, trans_a, trans_b, _tensor_key(b), _tensor_key(bias), _tensor_key(scale),
         _tensor_key(shift), None if block_sizes is None else tuple(block_sizes), out_dtype, split_k, explicit_split,
-        epilogue,
+        epilogue, force_kernel,
     )
 
     def build() -> GemmPlan:
@@ -474,9 +487,23 @@ def _matmul_plan(
             lda=int(a.shape[1]), ldb=int(b.shape[1]),
             bias=bias, scale=scale, shift=shift, epilogue=epilogue, out_dtype=out_dtype,
             split_k=split_k, parallel_split=split_k > 1 and not explicit_split, tiles=block_sizes,
+            force_kernel=force_kernel,
         )
 
     return _cached_plan(key, build)
+
+
+def tune_key(dtype: torch.dtype, m: int, n: int, k: int, trans_a: bool, trans_b: bool, has_bias: bool,
+             epilogue: Callable[[Tensor], Tensor]) -> str:
+    """The tuning-table key of a :func:`matmul` problem: sizes, layouts and the fused epilogue."""
+    fused = epilogues.resolve(epilogue)
+    tail = ("bias+" if has_bias else "") + ("unfused" if fused is None else f"act{fused[0]}")
+    return tuning.problem_key("matmul", dtype, m, n, k, trans_a, trans_b, 1, tail)
+
+
+def forget_plans() -> None:
+    """Drops the cached launch plans (after the tuning table changed)."""
+    _PLANS.clear()
 
 
 def matmul(
@@ -491,6 +518,7 @@ def matmul(
     shift: Tensor | None = None,
     out_dtype: torch.dtype | None = None,
     split_k: int | None = None,
+    _choice: tuning.Choice | None = None,
 ) -> Tensor:
     """``epilogue((op(A) @ op(B) + bias) * scale + shift)``, ``op`` transposing
     with ``trans_a``/``trans_b``.
@@ -523,7 +551,7 @@ def matmul(
         raise ValueError(f"bias must have shape ({n},), got {tuple(bias.shape)}")
     bias = None if bias is None else bias.to(device=a.device).contiguous()
     scale, shift = _affine_vector(scale, n, a), _affine_vector(shift, n, a)
-    plan = _matmul_plan(a, b, trans_a, trans_b, bias, epilogue, block_sizes, scale, shift, out_dtype, split_k)
+    plan = _matmul_plan(a, b, trans_a, trans_b, bias, epilogue, block_sizes, scale, shift, out_dtype, split_k, _choice)
     trace(f"matmul {tuple(a.shape)} x {tuple(b.shape)}")
     return plan.run(a, b, bias, scale, shift)
 
