@@ -30,8 +30,9 @@ SOURCES = [
     "gemm_simt.cu",
     "gemm_umma.cu",
     "host_rows.cu",
+    "attention.cu",
 ]
-HEADERS = ["common.cuh", "gemm_common.cuh", "../../include/b200ops.h"]
+HEADERS = ["common.cuh", "gemm_common.cuh", "umma_ptx.cuh", "../../include/b200ops.h"]
 FLAGS = [
     "-gencode",
     "arch=compute_100a,code=sm_100a",

@@ -127,6 +127,10 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "b200_gemm_workspace_bytes": (c_size_t, [ctypes.POINTER(GemmDesc)]),
     "b200_gemm_host_rows": (c_int, [ctypes.POINTER(GemmDesc), c_void_p, c_void_p, c_int64, c_void_p]),
     "b200_host_rows_release": (c_int, []),
+    "b200_attention": (
+        c_int,
+        [c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_float, c_void_p],
+    ),
     "b200_pack": (
         c_int,
         [c_int32, c_int32, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int32, c_void_p],

@@ -8,6 +8,7 @@ epilogue helpers. Every operator enqueues hand-written sm_100a kernels from
 
 from __future__ import annotations
 
+from .attention import attention
 from .elementwise import leaky_relu
 from .elementwise import relu
 from .elementwise import scalar_mul
@@ -65,6 +66,7 @@ __all__ = [
     "AffineLinearCache",
     "LinearCache",
     "add_extra",
+    "attention",
     "bmm",
     "cache_prepacked_weights",
     "column_sharded_linear",

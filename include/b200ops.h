@@ -149,6 +149,18 @@ int b200_gemm_host_rows(const b200_gemm_desc* desc, const void* a_host, void* c_
 /* Waits for the copy streams of the current device and frees its staging ring. */
 int b200_host_rows_release(void);
 
+/* Softmax attention per head: out[h] = softmax(scale * q[h] k[h]^T) v[h], the
+ * online-softmax kernel the reference's tests carry as a Helion body
+ * (tests/harness.py:263-300 `_attention`, tests/test_numerics.py:141-158
+ * `attention`). q, out: [heads, seq_q, dim]; k, v: [heads, seq_k, dim]; all
+ * contiguous bf16 (B200_BF16 is the only dtype; others are refused with
+ * B200_E_DTYPE and the host side composes the operators instead), dim 64 or 128,
+ * 16-byte aligned. Scores and the output accumulate in f32; the probabilities
+ * are rounded to bf16 for the second product, as the body's `p.to(q.dtype)` does.
+ * seq_k == 0 writes zeros. */
+int b200_attention(int32_t dtype, const void* q, const void* k, const void* v, void* out, int64_t heads,
+                   int64_t seq_q, int64_t seq_k, int64_t dim, float scale, void* stream);
+
 /* Layout conversions (bit-exact copies with zero fill). `kind`: */
 enum {
   B200_PACK_PAD_2D = 0,         /* [r,c] -> [rows_pad, cols_pad]                       matmul.py:78-89 */

@@ -315,6 +315,23 @@ def leaky_relu(x: Tensor, negative_slope: float = 0.01) -> Tensor:
     return torch.nn.functional.leaky_relu(x, negative_slope)
 
 
+def attention(q: Tensor, k: Tensor, v: Tensor, scale: float) -> Tensor:
+    """softmax(scale * q k^T) v per head of [heads, seq, dim] operands, as the online
+    loop of tests/harness.py:263-300 (`_attention`) computes it: scores and sums in
+    f32 or wider, the probabilities rounded to q.dtype before the second product
+    (`p.to(q.dtype)`, :297), one division at the end (:298). The running-maximum
+    rescaling of that loop only changes by which power of e numerator and
+    denominator are scaled, so the plain two-pass form below is the same function."""
+    scores = torch.einsum("hqd,hkd->hqk", q.double(), k.double()) * scale
+    if scores.shape[-1] == 0:
+        return torch.zeros_like(q)
+    top = scores.amax(-1, keepdim=True)
+    p = torch.exp(scores - top)
+    total = p.sum(-1, keepdim=True)
+    acc = torch.einsum("hqk,hkd->hqd", p.to(q.dtype).double(), v.double())
+    return (acc / total).to(q.dtype)
+
+
 def scalar_mul(a: Tensor, s: float) -> Tensor:
     """elementwise.py:34-39."""
     return a * s

@@ -278,6 +278,7 @@ def install_stand_in() -> None:
     language.tile = hl_tile
     language.zeros = hl_zeros
     language.full = hl_full
+    language.grid = lambda extent: range(int(_unwrap(extent)))
     language.specialize = lambda value: value
     language.register_block_size = hl_register_block_size
     language.constexpr = ConstExpr
@@ -327,6 +328,64 @@ def save(name: str, **tensors: torch.Tensor) -> None:
 
 def randn(generator: torch.Generator, *shape: int, dtype: torch.dtype = torch.float32, scale: float = 1.0):
     return (torch.randn(*shape, generator=generator) * scale).to(dtype)
+
+
+def load_functions(path: Path, names: list[str], namespace: dict[str, object]) -> dict[str, object]:
+    """Executes the named top-level functions and constants of a reference source file
+    (and nothing else of it) in ``namespace``: for files whose imports are not installed."""
+    import ast
+
+    tree = ast.parse(path.read_text())
+    wanted = []
+    for node in tree.body:
+        if isinstance(node, ast.FunctionDef) and node.name in names:
+            wanted.append(node)
+        elif isinstance(node, ast.Assign) and any(isinstance(t, ast.Name) and t.id in names for t in node.targets):
+            wanted.append(node)
+    module = ast.Module(body=wanted, type_ignores=[])
+    exec(compile(module, str(path), "exec"), namespace)
+    return namespace
+
+
+class _WideningTorch:
+    """``torch`` for an executed body, except that ``einsum`` of operands of different
+    float types widens them first: the compiled contraction takes a bf16 tile and
+    accumulates in f32, eager einsum refuses mixed types."""
+
+    def __getattr__(self, name: str) -> object:
+        return getattr(torch, name)
+
+    @staticmethod
+    def einsum(equation: str, *operands: torch.Tensor) -> torch.Tensor:
+        widest = max((o.dtype for o in operands), key=lambda d: torch.finfo(d).bits)
+        return torch.einsum(equation, *[o.to(widest) for o in operands])
+
+
+def attention_cases(reference: str, g: torch.Generator) -> None:
+    """The online-softmax attention body of the reference's tests, run block by block."""
+    language = sys.modules["helion.language"]
+    namespace = load_functions(
+        Path(reference) / "tests" / "harness.py",
+        ["_RESCALE_THRESHOLD", "_dot_nt", "_dot_nn", "_attention"],
+        {"torch": _WideningTorch(), "hl": language, "__builtins__": __builtins__},
+    )
+    body = namespace["_attention"]
+    bf16 = torch.bfloat16
+    cases: dict[str, torch.Tensor] = {}
+    for tag, (heads, seq, dim, blocks, dtype, spread) in {
+        "d64": (3, 256, 64, [64, 128], bf16, 1.0),
+        "d128": (2, 128, 128, [128, 64], bf16, 1.0),
+        "peaky": (2, 256, 64, [128, 32], bf16, 6.0),  # maxima that grow past the rescale threshold
+        "f32": (2, 96, 32, [32, 32], torch.float32, 1.0),
+    }.items():
+        q = randn(g, heads, seq, dim, dtype=dtype, scale=spread)
+        k = randn(g, heads, seq, dim, dtype=dtype, scale=spread)
+        v = randn(g, heads, seq, dim, dtype=dtype)
+        scale = dim ** -0.5
+        out = Kernel(body, config=Config(block_sizes=blocks))(q, k, v, ConstExpr(scale), ConstExpr(False))
+        cases.update({f"{tag}_q": q, f"{tag}_k": k, f"{tag}_v": v, f"{tag}_out": out,
+                      f"{tag}_scale": torch.tensor(scale)})
+    save("attention", **cases)
 
 
 def main(reference: str) -> None:
@@ -543,6 +602,7 @@ def main(reference: str) -> None:
         relu_bf16=ref.relu(xb),
         scaled_bf16=ref.scalar_mul(xb, torch.tensor(0.3)),
     )
+    attention_cases(reference, g)
     print("done")
 
 

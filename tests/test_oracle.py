@@ -164,3 +164,13 @@ def test_rms_norm_definition() -> None:
     torch.manual_seed(3)
     x, w = torch.randn(9, 40), torch.randn(40)
     assert checks.rel_frobenius(ops.rms_norm(x, w, 1e-5), F.rms_norm(x, (40,), w, 1e-5)) < 1e-6
+
+
+@pytest.mark.parametrize("tag", ["d64", "d128", "peaky", "f32"])
+def test_attention_against_the_reference_body(tag: str) -> None:
+    """The two-pass oracle against the reference's online loop run block by block."""
+    g = load_golden("attention")
+    q, k, v, want = (g[f"{tag}_{name}"] for name in ("q", "k", "v", "out"))
+    got = ops.attention(q, k, v, float(g[f"{tag}_scale"]))
+    assert got.dtype == want.dtype and got.shape == want.shape
+    checks.assert_parity(q.dtype, got, want.double() if q.dtype == torch.float32 else want.float(), f"attention {tag}")
