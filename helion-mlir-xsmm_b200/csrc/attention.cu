@@ -2,19 +2,27 @@
 // and out, online over 128-key blocks (the kernel the reference's tests carry as a
 // Helion body: tests/harness.py:263-300, tests/test_numerics.py:141-158).
 //
-// One CTA per (head, 128-query tile), 6 warps:
-//   warps 0-3  softmax: thread r owns query row r (TMEM lane r). Per key block it
-//              loads its 128 scores from TMEM, keeps a running maximum and sum,
-//              writes P = exp2(score * scale * log2e - max) as bf16 into shared memory
-//              in the tensor core's K-major swizzled layout, and rescales the output
-//              accumulator only when some row's maximum grew by more than 2^8 (the
-//              reference body's _RESCALE_THRESHOLD idea: a stale maximum only scales
-//              numerator and denominator alike). At the end: O / sum -> bf16 -> global.
-//   warp 4     TMA producer: Q once, then K and V blocks through two stages each.
-//   warp 5     MMA issuer (one lane): S_j = Q K_j^T into one of two TMEM score
-//              buffers, issued one block ahead so that it runs under the softmax of
-//              block j-1; then O += P_j V_j.
-// TMEM: columns [0,128) and [128,256) scores, [256, 256+D) output accumulator.
+// One CTA per (head, 128-query tile), 10 warps:
+//   warps 0-3  softmax group 0: the even key blocks.  Thread r owns query row r
+//   warps 4-7  softmax group 1: the odd key blocks.   (TMEM lane r) in both groups.
+//              Per block a thread loads its 128 scores from the group's TMEM score
+//              buffer, keeps the group's running maximum and sum of its row, writes
+//              P = exp2(score * scale * log2e - max) as bf16 into the group's shared
+//              memory tile in the tensor core's K-major swizzled layout, and rescales
+//              the group's output accumulator only when some row's maximum grew by
+//              more than 2^8 (the reference body's _RESCALE_THRESHOLD idea: a stale
+//              maximum only scales numerator and denominator alike). The two groups
+//              are half a block out of phase, so one group's exponentials (MUFU)
+//              run under the other's loads, maxima, conversions and stores, and the
+//              tensor core always has the other group's products to do.
+//              At the end the groups' (maximum, sum, accumulator) are merged:
+//              out = (O0 w0 + O1 w1) / (sum0 w0 + sum1 w1), w = 2^(max - common max).
+//   warp 8     TMA producers: lane 0 loads Q once and the K blocks, lane 1 the V blocks
+//   warp 9     MMA issuer (one lane): S_j = Q K_j^T into score buffer j % 2, issued
+//              two blocks ahead (as soon as the group has S_{j-2} in registers);
+//              O_{j%2} += P_j V_j when the group has written P_j.
+// TMEM: columns [0,128) and [128,256) scores, [256, 256+D) and [256+D, 256+2D) the
+// two output accumulators.
 //
 // Keys past the end of the sequence arrive as zeros from TMA and are masked to
 // -inf before the maximum; query rows past the end are computed and not stored.
@@ -30,10 +38,10 @@ namespace {
 
 constexpr int kRows = 128;      // queries per CTA
 constexpr int kKeys = 128;      // keys per block
-constexpr int kStages = 2;      // K and V stages
-constexpr int kSoftmaxWarps = 4;
-constexpr int kAttnProducerWarp = 4, kAttnMmaWarp = 5;
-constexpr int kAttnThreads = 32 * 6;
+constexpr int kMaxStages = 4;   // K and V stages: 2 at head size 128, 4 at 64
+constexpr int kGroupWarps = 4;  // warps of one softmax group
+constexpr int kAttnProducerWarp = 8, kAttnMmaWarp = 9;
+constexpr int kAttnThreads = 32 * 10;
 constexpr uint32_t kScoreCols = 128, kOutCol = 256;
 constexpr float kRescaleLog2 = 8.0f;
 constexpr int kErrAttnProducer = 32, kErrAttnMma = 64, kErrAttnSoftmax = 128;
@@ -49,10 +57,11 @@ struct AttnParams {
 
 struct __align__(8) AttnBarriers {
   uint64_t q_full;
-  uint64_t k_full[kStages], k_empty[kStages];
-  uint64_t v_full[kStages], v_empty[kStages];
-  uint64_t s_full[2], s_empty[2];
-  uint64_t p_full, pv_done;
+  uint64_t k_full[kMaxStages], k_empty[kMaxStages];
+  uint64_t v_full[kMaxStages], v_empty[kMaxStages];
+  uint64_t s_full[2], s_empty[2];  // per score buffer = per group
+  uint64_t p_full[2], pv_done[2];  // per group
+  uint64_t merge[4];               // the two warps of a TMEM lane quarter meet here at the end
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -67,15 +76,17 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                      const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
   constexpr int kChunks = D / 64;                       // 64-element column chunks of a D-wide tile
+  constexpr int kStages = D == 64 ? 4 : 2;              // what fits beside Q and P in shared memory
   constexpr uint32_t kTileBytes = kChunks * 16384;      // 128 rows x D bf16
   constexpr uint32_t kVHalfBytes = kChunks * 8192;      // 64 keys x D bf16 (MN-major chunks of 8 KiB)
+  constexpr uint32_t kPBytes = 32768;                   // 128 rows x 128 keys bf16, two K-major chunks
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t q_smem = smem_base;
   const uint32_t k_smem = q_smem + kTileBytes;
   const uint32_t v_smem = k_smem + kStages * kTileBytes;
-  const uint32_t p_smem = v_smem + kStages * kTileBytes;  // 2 chunks x 16 KiB
-  AttnBarriers* bars = reinterpret_cast<AttnBarriers*>(smem_raw + (p_smem + 32768u - smem_u32(smem_raw)));
+  const uint32_t p_smem = v_smem + kStages * kTileBytes;  // one tile per group
+  AttnBarriers* bars = reinterpret_cast<AttnBarriers*>(smem_raw + (p_smem + 2 * kPBytes - smem_u32(smem_raw)));
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -85,18 +96,19 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&bars->q_full), 1);
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < kMaxStages; ++s) {
       mbar_init(smem_u32(&bars->k_full[s]), 1);
       mbar_init(smem_u32(&bars->k_empty[s]), 1);
       mbar_init(smem_u32(&bars->v_full[s]), 1);
       mbar_init(smem_u32(&bars->v_empty[s]), 1);
     }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(smem_u32(&bars->s_full[s]), 1);
-      mbar_init(smem_u32(&bars->s_empty[s]), kSoftmaxWarps);
+    for (int g = 0; g < 2; ++g) {
+      mbar_init(smem_u32(&bars->s_full[g]), 1);
+      mbar_init(smem_u32(&bars->s_empty[g]), kGroupWarps);
+      mbar_init(smem_u32(&bars->p_full[g]), kGroupWarps);
+      mbar_init(smem_u32(&bars->pv_done[g]), 1);
     }
-    mbar_init(smem_u32(&bars->p_full), kSoftmaxWarps);
-    mbar_init(smem_u32(&bars->pv_done), 1);
+    for (int s = 0; s < 4; ++s) mbar_init(smem_u32(&bars->merge[s]), 2);
     bars->abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&map_q);
@@ -113,46 +125,47 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   const uint32_t tmem_base = bars->tmem_base;
 
   if (warp == kAttnProducerWarp) {
-    // ---------------------------------------------------------------- TMA producer
+    // ---------------------------------------------------------------- TMA producers
+    // Lane 0 loads Q and the K blocks, lane 1 the V blocks, each in its own loop: a K
+    // stage is free as soon as its scores are computed, a V stage only after its P V,
+    // and neither load may queue behind the other's wait.
     if (lane == 0) {
       const uint32_t qf = smem_u32(&bars->q_full);
       mbar_expect_tx(qf, kTileBytes);
       for (int c = 0; c < kChunks; ++c) tma_load_3d(q_smem + c * 16384, &map_q, qf, 64 * c, q0, head);
-      bool ok = true;
       uint32_t stage = 0, parity = 1;  // a fresh barrier's preceding phase counts as complete
-      int issued = 0;
-      for (int j = 0; j < nb && ok; ++j) {
-        const int key0 = j * kKeys;
-        ok = mbar_wait(smem_u32(&bars->k_empty[stage]), parity, abort_flag, p.status, kErrAttnProducer);
-        if (!ok) break;
+      for (int j = 0; j < nb; ++j) {
+        if (!mbar_wait(smem_u32(&bars->k_empty[stage]), parity, abort_flag, p.status, kErrAttnProducer)) break;
         const uint32_t kf = smem_u32(&bars->k_full[stage]);
         mbar_expect_tx(kf, kTileBytes);
         for (int c = 0; c < kChunks; ++c)
-          tma_load_3d(k_smem + stage * kTileBytes + c * 16384, &map_k, kf, 64 * c, key0, head);
-        ok = mbar_wait(smem_u32(&bars->v_empty[stage]), parity, abort_flag, p.status, kErrAttnProducer);
-        if (!ok) {
-          // K of this stage is in flight: wait for it below
-          ++issued;
-          break;
-        }
-        const uint32_t vf = smem_u32(&bars->v_full[stage]);
-        mbar_expect_tx(vf, kTileBytes);
-        for (int h = 0; h < 2; ++h)
-          for (int c = 0; c < kChunks; ++c)
-            tma_load_3d(v_smem + stage * kTileBytes + h * kVHalfBytes + c * 8192, &map_v, vf, 64 * c, key0 + 64 * h,
-                        head);
-        ++issued;
+          tma_load_3d(k_smem + stage * kTileBytes + c * 16384, &map_k, kf, 64 * c, j * kKeys, head);
         if (++stage == kStages) {
           stage = 0;
           parity ^= 1u;
         }
       }
-      if (*abort_flag) {
-        // Loads this CTA armed may still be in flight: give them (bounded) time to land
-        // before the shared memory is given up. On the regular path every block was consumed.
-        const unsigned long long start = global_ns();
-        while (global_ns() - start < 2000000ull) {
+    } else if (lane == 1) {
+      uint32_t stage = 0, parity = 1;
+      for (int j = 0; j < nb; ++j) {
+        if (!mbar_wait(smem_u32(&bars->v_empty[stage]), parity, abort_flag, p.status, kErrAttnProducer)) break;
+        const uint32_t vf = smem_u32(&bars->v_full[stage]);
+        mbar_expect_tx(vf, kTileBytes);
+        for (int h = 0; h < 2; ++h)
+          for (int c = 0; c < kChunks; ++c)
+            tma_load_3d(v_smem + stage * kTileBytes + h * kVHalfBytes + c * 8192, &map_v, vf, 64 * c,
+                        j * kKeys + 64 * h, head);
+        if (++stage == kStages) {
+          stage = 0;
+          parity ^= 1u;
         }
+      }
+    }
+    if (lane < 2 && *abort_flag) {
+      // Loads this CTA armed may still be in flight: give them (bounded) time to land
+      // before the shared memory is given up. On the regular path every block was consumed.
+      const unsigned long long start = global_ns();
+      while (global_ns() - start < 2000000ull) {
       }
     }
     __syncwarp();
@@ -163,11 +176,12 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       bool ok = mbar_wait(smem_u32(&bars->q_full), 0, abort_flag, p.status, kErrAttnMma);
       tc_fence_after();
       const uint64_t q_desc = make_desc(q_smem, 1u, hi);
-      // S_j = Q K_j^T: both operands K-major, D/16 MMAs of K = 16 (4 per 64-wide chunk).
+      // S_j = Q K_j^T into score buffer j % 2: both operands K-major, D/16 MMAs of K = 16.
+      // The buffer is free once its group holds S_{j-2} in registers.
       auto issue_scores = [&](int j) -> bool {
-        const uint32_t st = j % kStages, buf = j & 1;
+        const uint32_t st = j % kStages, g = j & 1;
         if (!mbar_wait(smem_u32(&bars->k_full[st]), (j / kStages) & 1, abort_flag, p.status, kErrAttnMma)) return false;
-        if (!mbar_wait(smem_u32(&bars->s_empty[buf]), ((j >> 1) & 1) ^ 1, abort_flag, p.status, kErrAttnMma))
+        if (!mbar_wait(smem_u32(&bars->s_empty[g]), ((j >> 1) & 1) ^ 1, abort_flag, p.status, kErrAttnMma))
           return false;
         tc_fence_after();
         const uint64_t k_desc = make_desc(k_smem + st * kTileBytes, 1u, hi);
@@ -177,87 +191,109 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const uint64_t step = static_cast<uint64_t>((c * 16384 + i * 32) >> 4);
-            umma_bf16<1>(tmem_base + buf * kScoreCols, q_desc + step, k_desc + step, p.idesc_qk, accumulate);
+            umma_bf16<1>(tmem_base + g * kScoreCols, q_desc + step, k_desc + step, p.idesc_qk, accumulate);
             accumulate = 1;
           }
         }
         umma_commit<1>(smem_u32(&bars->k_empty[st]));
-        umma_commit<1>(smem_u32(&bars->s_full[buf]));
+        umma_commit<1>(smem_u32(&bars->s_full[g]));
         return true;
       };
       if (ok && nb > 0) ok = issue_scores(0);
+      if (ok && nb > 1) ok = issue_scores(1);
       for (int j = 0; j < nb && ok; ++j) {
-        if (j + 1 < nb) {
-          ok = issue_scores(j + 1);
+        if (j + 2 < nb) {
+          ok = issue_scores(j + 2);
           if (!ok) break;
         }
-        // O += P_j V_j: P K-major (two 64-key chunks), V MN-major (64-key halves of D/64 chunks).
-        const uint32_t st = j % kStages;
+        // O_g += P_j V_j: P K-major (two 64-key chunks), V MN-major (64-key halves of D/64 chunks).
+        const uint32_t st = j % kStages, g = j & 1;
         ok = mbar_wait(smem_u32(&bars->v_full[st]), (j / kStages) & 1, abort_flag, p.status, kErrAttnMma);
-        if (ok) ok = mbar_wait(smem_u32(&bars->p_full), j & 1, abort_flag, p.status, kErrAttnMma);
+        if (ok) ok = mbar_wait(smem_u32(&bars->p_full[g]), (j >> 1) & 1, abort_flag, p.status, kErrAttnMma);
         if (!ok) break;
         tc_fence_after();
-        uint32_t accumulate = j > 0 ? 1u : 0u;
+        uint32_t accumulate = j > 1 ? 1u : 0u;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          const uint64_t p_desc = make_desc(p_smem + h * 16384, 1u, hi);
+          const uint64_t p_desc = make_desc(p_smem + g * kPBytes + h * 16384, 1u, hi);
           const uint64_t v_desc = make_desc(v_smem + st * kTileBytes + h * kVHalfBytes, 8192u >> 4, hi);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            umma_bf16<1>(tmem_base + kOutCol, p_desc + static_cast<uint64_t>((i * 32) >> 4),
+            umma_bf16<1>(tmem_base + kOutCol + g * D, p_desc + static_cast<uint64_t>((i * 32) >> 4),
                          v_desc + static_cast<uint64_t>((i * 2048) >> 4), p.idesc_pv, accumulate);
             accumulate = 1;
           }
         }
         umma_commit<1>(smem_u32(&bars->v_empty[st]));
-        umma_commit<1>(smem_u32(&bars->pv_done));
+        umma_commit<1>(smem_u32(&bars->pv_done[g]));
       }
     }
     __syncwarp();
   } else {
     // ---------------------------------------------------------------- softmax + output
-    const int row = warp * 32 + lane;  // TMEM lane = query row of the tile
-    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const int quarter = warp & 3, g = warp >> 2;
+    const int row = quarter * 32 + lane;  // TMEM lane = query row of the tile
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t score_addr = tmem_base + lane_addr + g * kScoreCols;
+    const uint32_t out_addr = tmem_base + lane_addr + kOutCol + g * D;
     float top = -1.0e30f, total = 0.f;
+    const bool negative = p.scale_log2 < 0.f;  // then the largest scaled score is the smallest raw one
     bool ok = true;
-    const uint32_t p_row = p_smem + row * 128;
+    const uint32_t p_row = p_smem + g * kPBytes + row * 128;
     const uint32_t swz = static_cast<uint32_t>(row & 7);
-    for (int j = 0; j < nb && ok; ++j) {
-      const uint32_t buf = j & 1;
-      ok = mbar_wait(smem_u32(&bars->s_full[buf]), (j >> 1) & 1, abort_flag, p.status, kErrAttnSoftmax);
+    const uint32_t s_full = smem_u32(&bars->s_full[g]), s_empty = smem_u32(&bars->s_empty[g]);
+    const uint32_t p_full = smem_u32(&bars->p_full[g]), pv_done = smem_u32(&bars->pv_done[g]);
+    int mine = 0;  // blocks this group has taken
+    for (int j = g; j < nb && ok; j += 2, ++mine) {
+      ok = mbar_wait(s_full, mine & 1, abort_flag, p.status, kErrAttnSoftmax);
       ok = __all_sync(0xffffffffu, ok) != 0;
       if (!ok) break;
       tc_fence_after();
+      // All 128 scores of this row (unscaled), one wait for the four loads.
       float s[kKeys];
+      {
+        uint32_t(&raw)[kKeys] = reinterpret_cast<uint32_t(&)[kKeys]>(s);
 #pragma unroll
-      for (int c = 0; c < kKeys / 32; ++c) {
-        uint32_t raw[32];
-        tmem_ld_32x32(tmem_base + lane_addr + buf * kScoreCols + c * 32, raw);
+        for (int c = 0; c < kKeys / 32; ++c)
+          tmem_ld_32x32(score_addr + c * 32, reinterpret_cast<uint32_t(&)[32]>(raw[c * 32]));
         tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(raw[i]) * p.scale_log2;
       }
-      // The scores are in registers: the MMA warp may overwrite this buffer with S_{j+2}.
+      // The scores are in registers: the MMA warp may overwrite the buffer with S_{j+2}.
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bars->s_empty[buf]));
+      if (lane == 0) mbar_arrive(s_empty);
       const int valid = p.seq_k - j * kKeys;  // keys of this block that exist
       if (valid < kKeys) {
+        const float masked = negative ? INFINITY : -INFINITY;  // times the scale: -inf
 #pragma unroll
         for (int i = 0; i < kKeys; ++i)
-          if (i >= valid) s[i] = -INFINITY;
+          if (i >= valid) s[i] = masked;
       }
-      float block_top = s[0];
+      // Row maximum of scale * s in eight independent chains.
+      float part[8];
 #pragma unroll
-      for (int i = 1; i < kKeys; ++i) block_top = fmaxf(block_top, s[i]);
-      const float new_top = fmaxf(top, block_top);
+      for (int i = 0; i < 8; ++i) part[i] = s[i];
+      if (!negative) {
+#pragma unroll
+        for (int i = 8; i < kKeys; ++i) part[i & 7] = fmaxf(part[i & 7], s[i]);
+#pragma unroll
+        for (int i = 4; i > 0; i >>= 1)
+          for (int t = 0; t < i; ++t) part[t] = fmaxf(part[t], part[t + i]);
+      } else {
+#pragma unroll
+        for (int i = 8; i < kKeys; ++i) part[i & 7] = fminf(part[i & 7], s[i]);
+#pragma unroll
+        for (int i = 4; i > 0; i >>= 1)
+          for (int t = 0; t < i; ++t) part[t] = fminf(part[t], part[t + i]);
+      }
+      const float new_top = fmaxf(top, part[0] * p.scale_log2);
       bool waited_pv = false;
-      if (j == 0) {
+      if (mine == 0) {
         top = new_top;
       } else if (__any_sync(0xffffffffu, new_top - top > kRescaleLog2)) {
-        // Some row of this warp outgrew its maximum: rescale the warp's rows of O
-        // (after the previous P V has landed there) and their sums.
-        ok = mbar_wait(smem_u32(&bars->pv_done), (j - 1) & 1, abort_flag, p.status, kErrAttnSoftmax);
+        // Some row of this warp outgrew its maximum: rescale the warp's rows of the
+        // group's accumulator (after the group's previous P V has landed there) and sums.
+        ok = mbar_wait(pv_done, (mine - 1) & 1, abort_flag, p.status, kErrAttnSoftmax);
         ok = __all_sync(0xffffffffu, ok) != 0;
         if (!ok) break;
         waited_pv = true;
@@ -265,27 +301,30 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         const float alpha = fast_exp2(top - new_top);
         total *= alpha;
         top = new_top;
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t raw[32];
-          tmem_ld_32x32(tmem_base + lane_addr + kOutCol + c * 32, raw);
+#pragma unroll 1
+        for (int c = 0; c < D / 16; ++c) {  // 16 columns at a time: the scores hold most registers
+          uint32_t raw[16];
+          tmem_ld_32x16(out_addr + c * 16, raw);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * alpha);
-          tmem_st_32x32(tmem_base + lane_addr + kOutCol + c * 32, raw);
+          for (int i = 0; i < 16; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * alpha);
+          tmem_st_32x16(out_addr + c * 16, raw);
         }
         tmem_st_wait();
       }
-      float sum = 0.f;
+      // p = 2^(scale * s - top): one FFMA and one ex2 per score, sums in eight chains.
+      const float neg_top = -top;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) part[i] = 0.f;
 #pragma unroll
       for (int i = 0; i < kKeys; ++i) {
-        s[i] = fast_exp2(s[i] - top);
-        sum += s[i];
+        s[i] = fast_exp2(fmaf(s[i], p.scale_log2, neg_top));
+        part[i & 7] += s[i];
       }
-      total += sum;
-      // P_{j-1} has been consumed (its P V completed) before P_j overwrites it.
-      if (j > 0 && !waited_pv) {
-        ok = mbar_wait(smem_u32(&bars->pv_done), (j - 1) & 1, abort_flag, p.status, kErrAttnSoftmax);
+      total += ((part[0] + part[1]) + (part[2] + part[3])) + ((part[4] + part[5]) + (part[6] + part[7]));
+      // The group's previous P has been consumed (its P V completed) before this one overwrites it.
+      if (mine > 0 && !waited_pv) {
+        ok = mbar_wait(pv_done, (mine - 1) & 1, abort_flag, p.status, kErrAttnSoftmax);
         ok = __all_sync(0xffffffffu, ok) != 0;
         if (!ok) break;
       }
@@ -303,36 +342,67 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       fence_proxy_async();  // generic-proxy writes of P become visible to the tensor core
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bars->p_full));
+      if (lane == 0) mbar_arrive(p_full);
     }
-    if (ok && nb > 0) {
-      ok = mbar_wait(smem_u32(&bars->pv_done), (nb - 1) & 1, abort_flag, p.status, kErrAttnSoftmax);
+    // The group's last P V has landed in its accumulator.
+    if (ok && mine > 0) {
+      ok = mbar_wait(pv_done, (mine - 1) & 1, abort_flag, p.status, kErrAttnSoftmax);
+      ok = __all_sync(0xffffffffu, ok) != 0;
+    }
+    // Merge the two groups: each row's (maximum, sum) goes through shared memory, the
+    // accumulators are read from TMEM by both warps of the lane quarter, each for its
+    // half of the output columns.
+    // (The statistics reuse the group's own P tile, which its last P V has finished reading.)
+    float2* stats = reinterpret_cast<float2*>(smem_raw + (p_smem - smem_u32(smem_raw)));  // [group] at g * kPBytes
+    if (ok) {
+      stats[g * (kPBytes / sizeof(float2)) + row] = make_float2(top, total);
+      tc_fence_before();
+      __syncwarp();
+      const uint32_t merge = smem_u32(&bars->merge[quarter]);
+      if (lane == 0) mbar_arrive(merge);
+      ok = mbar_wait(merge, 0, abort_flag, p.status, kErrAttnSoftmax);
       ok = __all_sync(0xffffffffu, ok) != 0;
     }
     if (ok) {
       tc_fence_after();
-      const float inv = nb > 0 ? 1.f / total : 0.f;
+      const float2 other = stats[(g ^ 1) * (kPBytes / sizeof(float2)) + row];
+      const int theirs = (nb - (g ^ 1) + 1) >> 1;  // blocks the other group took
+      const float common = fmaxf(top, other.x);
+      const float w_mine = mine > 0 ? fast_exp2(top - common) : 0.f;
+      const float w_theirs = theirs > 0 ? fast_exp2(other.x - common) : 0.f;
+      const float inv = 1.f / (total * w_mine + other.y * w_theirs);
+      const float a = w_mine * inv, b = w_theirs * inv;
       const int64_t q_row = static_cast<int64_t>(q0) + row;
       __nv_bfloat16* dst = p.out + (static_cast<int64_t>(head) * p.seq_q + q_row) * D;
+      const uint32_t theirs_addr = tmem_base + lane_addr + kOutCol + (g ^ 1) * D;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t raw[32];
-        if (nb > 0) {
-          tmem_ld_32x32(tmem_base + lane_addr + kOutCol + c * 32, raw);
-          tmem_ld_wait();
-        } else {
+      for (int c = 0; c < D / 64; ++c) {
+        const int col = g * (D / 2) + c * 32;
+        float o[32];
+        {
+          uint32_t x[32];
+          if (mine > 0) {
+            tmem_ld_32x32(out_addr + col, x);
+            tmem_ld_wait();
+          }
 #pragma unroll
-          for (int i = 0; i < 32; ++i) raw[i] = 0;
+          for (int i = 0; i < 32; ++i) o[i] = mine > 0 ? __uint_as_float(x[i]) * a : 0.f;
+          if (theirs > 0) {
+            tmem_ld_32x32(theirs_addr + col, x);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = fmaf(__uint_as_float(x[i]), b, o[i]);
+          }
         }
         if (q_row < p.seq_q) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             uint4 w;
-            w.x = pack2(__uint_as_float(raw[8 * i]) * inv, __uint_as_float(raw[8 * i + 1]) * inv);
-            w.y = pack2(__uint_as_float(raw[8 * i + 2]) * inv, __uint_as_float(raw[8 * i + 3]) * inv);
-            w.z = pack2(__uint_as_float(raw[8 * i + 4]) * inv, __uint_as_float(raw[8 * i + 5]) * inv);
-            w.w = pack2(__uint_as_float(raw[8 * i + 6]) * inv, __uint_as_float(raw[8 * i + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + c * 32 + 8 * i) = w;
+            w.x = pack2(o[8 * i], o[8 * i + 1]);
+            w.y = pack2(o[8 * i + 2], o[8 * i + 3]);
+            w.z = pack2(o[8 * i + 4], o[8 * i + 5]);
+            w.w = pack2(o[8 * i + 6], o[8 * i + 7]);
+            *reinterpret_cast<uint4*>(dst + col + 8 * i) = w;
           }
         }
       }
@@ -362,7 +432,8 @@ std::once_flag g_attn_attr_once[64];
 
 template <int D>
 size_t attn_smem_bytes() {
-  return 1024 + static_cast<size_t>(1 + 2 * kStages) * (D / 64) * 16384 + 32768 + sizeof(AttnBarriers);
+  const size_t stages = D == 64 ? 4 : 2;
+  return 1024 + (1 + 2 * stages) * (D / 64) * 16384 + 2 * 32768 + sizeof(AttnBarriers);
 }
 
 }  // namespace
@@ -376,6 +447,8 @@ extern "C" int b200_attention(int32_t dtype, const void* q, const void* k, const
   if (dtype != B200_BF16) return refuse(B200_E_DTYPE);
   if (heads < 0 || seq_q < 0 || seq_k < 0) return refuse(B200_E_SHAPE);
   if (dim != 64 && dim != 128) return refuse(B200_E_SHAPE);
+  // Keys past the end are masked as -inf * scale, which needs a non-zero finite scale.
+  if (!(scale != 0.f) || !(fabsf(scale) <= 3.0e38f)) return refuse(B200_E_ARG);
   if (heads == 0 || seq_q == 0) return finish(0);
   if (!q || !out || (seq_k > 0 && (!k || !v))) return refuse(B200_E_NULL);
   if (!aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16) || !aligned(out, 16)) return refuse(B200_E_ALIGN);

@@ -36,9 +36,10 @@ def _check(q: Tensor, k: Tensor, v: Tensor) -> tuple[int, int, int, int]:
     return heads, seq_q, int(k.shape[1]), dim
 
 
-def fused(q: Tensor, k: Tensor, v: Tensor) -> bool:
-    """Whether these operands take the fused kernel (else the composed path)."""
-    return q.dtype == torch.bfloat16 and q.dim() == 3 and int(q.shape[2]) in _FUSED_DIMS
+def fused(q: Tensor, k: Tensor, v: Tensor, scale: float = 1.0) -> bool:
+    """Whether this call takes the fused kernel (else the composed path)."""
+    return (q.dtype == torch.bfloat16 and q.dim() == 3 and int(q.shape[2]) in _FUSED_DIMS
+            and scale != 0.0 and math.isfinite(scale))
 
 
 def attention(q: Tensor, k: Tensor, v: Tensor, scale: float | None = None) -> Tensor:
@@ -48,7 +49,7 @@ def attention(q: Tensor, k: Tensor, v: Tensor, scale: float | None = None) -> Te
     device = native.require_cuda(q, k, v)
     scale = 1.0 / math.sqrt(dim) if scale is None else float(getattr(scale, "value", scale))
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-    if fused(q, k, v):
+    if fused(q, k, v, scale):
         out = output_pool.empty_like(q)
         with native.on_device(device):
             code = native.module().b200_attention(

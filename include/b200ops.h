@@ -157,7 +157,7 @@ int b200_host_rows_release(void);
  * B200_E_DTYPE and the host side composes the operators instead), dim 64 or 128,
  * 16-byte aligned. Scores and the output accumulate in f32; the probabilities
  * are rounded to bf16 for the second product, as the body's `p.to(q.dtype)` does.
- * seq_k == 0 writes zeros. */
+ * seq_k == 0 writes zeros. `scale` must be finite and non-zero (B200_E_ARG). */
 int b200_attention(int32_t dtype, const void* q, const void* k, const void* v, void* out, int64_t heads,
                    int64_t seq_q, int64_t seq_k, int64_t dim, float scale, void* stream);
 
