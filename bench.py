@@ -1,6 +1,6 @@
 """Benchmark of the hot path: the fused bf16 linear  y = GELU(x @ W^T + b).
 
-    python bench.py --gpus N --steps K --warmup W [--workload c2|c4|c1|c3|c5] [--impl reference]
+    python bench.py --gpus N --steps K --warmup W [--workload c2|c4|c1|c3|c5|attn] [--impl reference]
 
 A step is one pass of the hot path over one batch of synthetic input. The default
 workload is the configuration the headline metric is quoted on: x [8192,4096],
@@ -401,7 +401,52 @@ class SplitKBmm(Workload):
         return 2.0 * 2 * self.M * self.N * self.K / (time.perf_counter() - t0) / 1e12, "2 of 64 batches, torch CPU f32 bmm"
 
 
-WORKLOADS = {"c1": F32Matmul, "c2": LinearGelu, "c3": BlockedMatmul, "c4": RowNorms, "c5": SplitKBmm}
+class Attention(Workload):
+    """Softmax attention of 128 heads (4 sequences x 32 heads) of 4096 x 128, bf16."""
+
+    name, metric, unit, dtype, bound = "attention_128x4096x128", "bf16 attention TFLOP/s", "TFLOP/s", "bf16", "tensor"
+    H, S, D, SETS = 128, 4096, 128, 2
+
+    def setup(self, device: torch.device, rank: int) -> None:
+        import helion_mlir_utils as ops
+
+        self.ops = ops
+        gen = torch.Generator().manual_seed(1006 + rank)
+        host = [torch.randn(self.H, self.S, self.D, generator=gen).bfloat16() for _ in range(3)]
+        # Two rotating operand sets: 2 x 4 x 134 MB, beyond the 126 MB L2.
+        self.sets = _rotating(self.SETS, lambda i: [t.roll(i, 1).to(device) for t in host])
+        self.pinned = [t.pin_memory() for t in host]
+        self.out_pinned = torch.empty(self.H, self.S, self.D, dtype=torch.bfloat16).pin_memory()
+        self.stage = [torch.empty_like(t) for t in self.sets[0]]
+
+    def step(self, index: int) -> torch.Tensor:
+        q, k, v = self.sets[index % self.SETS]
+        return self.ops.attention(q, k, v)
+
+    def e2e_step(self, index: int) -> tuple[int, int]:
+        for dst, src in zip(self.stage, self.pinned):
+            dst.copy_(src, non_blocking=True)
+        self.out_pinned.copy_(self.ops.attention(*self.stage), non_blocking=True)
+        return 3 * self.pinned[0].numel() * 2, self.out_pinned.numel() * 2
+
+    def work_per_step(self) -> float:
+        return 4.0 * self.H * self.S * self.S * self.D
+
+    def config(self) -> dict[str, object]:
+        return {"workload": self.name, "heads": self.H, "seq": self.S, "dim": self.D, "scale": "dim ** -0.5",
+                "sharding": "heads per GPU, no collective", "l2": "operands rotated over 2 sets (1.07 GB) > 126 MB L2"}
+
+    def cpu_sample(self, threads: int) -> tuple[float, str]:
+        from oracle import ops as ref
+
+        heads = 2
+        q, k, v = (torch.randn(heads, self.S, self.D).bfloat16() for _ in range(3))
+        t0 = time.perf_counter()
+        ref.attention(q.float(), k.float(), v.float(), self.D ** -0.5)
+        return 4.0 * heads * self.S * self.S * self.D / (time.perf_counter() - t0) / 1e12, f"{heads} of {self.H} heads, torch CPU restatement (f64 scores)"
+
+
+WORKLOADS = {"c1": F32Matmul, "c2": LinearGelu, "c3": BlockedMatmul, "c4": RowNorms, "c5": SplitKBmm, "attn": Attention}
 
 
 # --------------------------------------------------------------------------- driver
@@ -461,7 +506,7 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=20)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
-    parser.add_argument("--rows", type=int, default=0, help="rows per GPU of the c2/c4 workloads (default: the configuration's; smaller sizes are for profiler captures, not for reported numbers)")
+    parser.add_argument("--rows", type=int, default=0, help="rows per GPU of the c2/c4 workloads, heads per GPU of attn (default: the configuration's; smaller sizes are for profiler captures, not for reported numbers)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-e2e", action="store_true")
     args = parser.parse_args()
@@ -471,6 +516,8 @@ def main() -> None:
     workload: Workload = WORKLOADS[args.workload]()
     if args.rows > 0 and hasattr(workload, "M"):
         workload.M = args.rows
+    if args.rows > 0 and hasattr(workload, "H"):
+        workload.H = args.rows
     if args.impl == "reference":
         run_reference(args, workload, rank)
         return
@@ -581,6 +628,7 @@ TRAFFIC: dict[str, float | None] = {
     "c3": None,
     "c4": 860.1e6,  # f32 softmax, scaled x4 from the 8192-row capture (134.26 MB read + 80.77 MB written)
     "c5": None,
+    "attn": None,
 }
 
 

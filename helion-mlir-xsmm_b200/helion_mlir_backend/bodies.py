@@ -161,6 +161,9 @@ def _make(block_sizes: tuple[int, ...] | None) -> dict[str, tuple[tuple[str, ...
         "_pack_b_vnni_kernel": (("b", "k_pad", "n_pad"), pack(ops.pack_b_blocked_vnni)),
         "_pack_b_vnni_kernel_t": (("b_t", "k_pad", "n_pad"), pack(ops.pack_b_blocked_vnni_t)),
         "_pack_b_vnni_panels_kernel_t": (("b3_t", "panel"), pack_panels),
+        # the attention bodies of the reference's tests (tests/harness.py:263, tests/test_numerics.py:141)
+        "_attention": (("q", "k", "v", "scale", "vnni"), lambda q, k, v, scale, vnni=False: ops.attention(q, k, v, float(_value(scale)))),
+        "attention": (("q", "k", "v"), lambda q, k, v: ops.attention(q, k, v, 1.0)),
     }
 
 
@@ -170,7 +173,7 @@ KNOWN_BODIES = frozenset(
     _matmul_prepacked_rows _split_k_partials _sum_partials _bmm_direct _bmm_batched _matvec_kernel _row_sum_kernel
     _row_dot_kernel _column_sum_kernel _relu_kernel _leaky_relu_kernel _scalar_mul_kernel _pad_kernel _pack_a_kernel
     _pack_a_kernel_t _pack_b_kernel _pack_b_kernel_t _pack_b_vnni_kernel _pack_b_vnni_kernel_t
-    _pack_b_vnni_panels_kernel_t""".split()
+    _pack_b_vnni_panels_kernel_t _attention attention""".split()
 )
 
 

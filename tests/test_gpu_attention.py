@@ -93,3 +93,19 @@ def test_c_abi_refusals(ops) -> None:
     assert lib.b200_attention(native.BF16, None, None, None, None, 2, 128, 128, 64, 1.0, None) == 6  # NULL
     assert lib.b200_attention(native.BF16, x.data_ptr() + 2, *args[1:], 2, 64, 64, 64, 1.0, None) == 4  # alignment
     assert lib.b200_attention(native.BF16, *args, 0, 128, 128, 64, 1.0, None) == 0  # nothing to do
+
+
+def test_reference_attention_bodies_are_recognised(ops) -> None:
+    """A kernel body named and parameterised like the reference's test kernels runs natively."""
+    from helion_mlir_backend import inject
+
+    namespace: dict = {}
+    exec("def _attention(q, k, v, scale, vnni):\n    raise AssertionError('never run')\n"
+         "def attention(q, k, v):\n    raise AssertionError('never run')", namespace)
+    g = load_golden("attention")
+    q, k, v, want = (g[f"d64_{name}"] for name in ("q", "k", "v", "out"))
+    run = inject.recognise(namespace["_attention"], {"block_sizes": [64, 128]})
+    assert run is not None
+    checks.assert_parity(BF16, run(*cuda(q, k, v), float(g["d64_scale"]), False).cpu(), want.float(), "_attention body")
+    plain = inject.recognise(namespace["attention"], None)
+    checks.assert_parity(BF16, plain(*cuda(q, k, v)).cpu(), ref.attention(q, k, v, 1.0).float(), "attention body")
