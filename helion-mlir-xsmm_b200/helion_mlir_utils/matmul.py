@@ -286,10 +286,11 @@ class GemmPlan:
         # f32 operands of plain layouts run as a widened bf16 GEMM built in scratch
         widened = d.dtype == native.F32 and d.a_layout <= native.LAYOUT_COL and d.b_layout <= native.LAYOUT_COL
         self._wants_workspace = packed or widened or (d.split_k > 1 and parallel_split)
+        self._workspace_need: int | None = None
 
     def run(self, a: Tensor, b: Tensor, bias: Tensor | None = None, scale: Tensor | None = None,
             shift: Tensor | None = None, out: Tensor | None = None) -> Tensor:
-        desc = self.desc
+        desc = native.GemmDesc.from_buffer_copy(self.desc)  # per call: plans are shared between threads
         if out is None:
             out = output_pool.empty(self.out_shape, dtype=self.out_dtype, device=self.device)
         vec = self.vec_dtype
@@ -302,7 +303,9 @@ class GemmPlan:
         workspace = None
         desc.workspace, desc.workspace_bytes = None, 0
         if self._wants_workspace:
-            need = int(lib.b200_gemm_workspace_bytes(ctypes.byref(desc)))
+            need = self._workspace_need
+            if need is None:  # a function of the planned sizes and layouts only
+                need = self._workspace_need = int(lib.b200_gemm_workspace_bytes(ctypes.byref(desc)))
             if need:
                 workspace = output_pool.empty((need,), dtype=torch.uint8, device=self.device)
                 desc.workspace, desc.workspace_bytes = workspace.data_ptr(), need
@@ -318,7 +321,7 @@ class GemmPlan:
                  out_host: Tensor, chunk_rows: int) -> Tensor:
         """The same GEMM with ``a_host`` read from and ``out_host`` written to host
         memory, row chunks streamed through the library's staging ring."""
-        desc = self.desc
+        desc = native.GemmDesc.from_buffer_copy(self.desc)
         vec = self.vec_dtype
         bias = None if bias is None else bias.to(vec)
         scale = None if scale is None else scale.to(vec)
@@ -458,35 +461,37 @@ def _matmul_plan(
     m = int(a.shape[1]) if trans_a else int(a.shape[0])
     n = int(b.shape[0]) if trans_b else int(b.shape[1])
     k = int(a.shape[0]) if trans_a else int(a.shape[1])
-    explicit_split = split_k is not None and split_k > 1
-    plain = bias is None and scale is None and shift is None and epilogue is identity_epilogue
-    # A measured choice for this problem on this hardware overrules the heuristics,
-    # unless the caller fixed the tiles or the split.
-    if choice is None and block_sizes is None and split_k is None and a.dtype == torch.bfloat16:
-        choice = tuning.lookup(tune_key(a.dtype, m, n, k, trans_a, trans_b, bias is not None, epilogue), a.device)
-    force_kernel = 0
-    if choice is not None:
-        if choice.tile_n:
-            block_sizes = (_TILE_M, choice.tile_n, _TILE_K)
-        force_kernel = choice.force_kernel()
-        if choice.split_k > 1 and plain and split_k is None:
-            split_k = choice.split_k
-    if split_k is None:
-        split_k = _split_k(m, n, k) if plain else 0
+    # Everything the plan depends on, as the caller gave it: the heuristics and the
+    # tuning table are only consulted when a problem is planned, not on every call.
     key = (
         "matmul", m, n, k, a.dtype, a.device, trans_a, trans_b, _tensor_key(b), _tensor_key(bias), _tensor_key(scale),
-        _tensor_key(shift), None if block_sizes is None else tuple(block_sizes), out_dtype, split_k, explicit_split,
-        epilogue, force_kernel,
+        _tensor_key(shift), None if block_sizes is None else tuple(block_sizes), out_dtype, split_k, epilogue, choice,
     )
 
     def build() -> GemmPlan:
+        tiles, splits, picked = block_sizes, split_k, choice
+        explicit_split = splits is not None and splits > 1
+        plain = bias is None and scale is None and shift is None and epilogue is identity_epilogue
+        # A measured choice for this problem on this hardware overrules the heuristics,
+        # unless the caller fixed the tiles or the split.
+        if picked is None and tiles is None and splits is None and a.dtype == torch.bfloat16:
+            picked = tuning.lookup(tune_key(a.dtype, m, n, k, trans_a, trans_b, bias is not None, epilogue), a.device)
+        force_kernel = 0
+        if picked is not None:
+            if picked.tile_n:
+                tiles = (_TILE_M, picked.tile_n, _TILE_K)
+            force_kernel = picked.force_kernel()
+            if picked.split_k > 1 and plain and splits is None:
+                splits = picked.split_k
+        if splits is None:
+            splits = _split_k(m, n, k) if plain else 0
         return _plan_gemm(
             a=a, m=m, n=n, k=k,
             a_layout=native.LAYOUT_COL if trans_a else native.LAYOUT_ROW,
             b_layout=native.LAYOUT_COL if trans_b else native.LAYOUT_ROW,
             lda=int(a.shape[1]), ldb=int(b.shape[1]),
             bias=bias, scale=scale, shift=shift, epilogue=epilogue, out_dtype=out_dtype,
-            split_k=split_k, parallel_split=split_k > 1 and not explicit_split, tiles=block_sizes,
+            split_k=splits, parallel_split=splits > 1 and not explicit_split, tiles=tiles,
             force_kernel=force_kernel,
         )
 

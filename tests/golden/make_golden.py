@@ -2,7 +2,7 @@
 
 Run in the build container, where the reference source tree is mounted:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path of the reference checkout>
 
 The reference's ``helion_mlir_utils`` cannot be imported as is (it needs Helion
 and an MLIR toolchain that are not installed). Its kernel *bodies* and host-side
@@ -607,4 +607,6 @@ def main(reference: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py <path of the reference checkout>")
+    main(sys.argv[1])
