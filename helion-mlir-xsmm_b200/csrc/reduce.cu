@@ -23,6 +23,8 @@ struct ReduceParams {
 };
 
 // KIND: 0 row_sum, 1 row_dot (v f32), 2 matvec (v of T)
+// `tpr` threads share a row (a power of two from 4 to 256): narrow rows put several
+// rows in one warp so that no lane idles, wide rows spread over up to 8 warps.
 template <typename T, bool VEC, int KIND>
 __global__ void __launch_bounds__(256) row_reduce_kernel(const ReduceParams p) {
   constexpr int EPV = VEC ? Elem<T>::kVec : 1;
@@ -38,6 +40,7 @@ __global__ void __launch_bounds__(256) row_reduce_kernel(const ReduceParams p) {
   T* out = reinterpret_cast<T*>(p.out);
   const float* vf = reinterpret_cast<const float*>(p.v);
   const T* vt = reinterpret_cast<const T*>(p.v);
+  const int64_t step = static_cast<int64_t>(tpr) * EPV;
 
   for (int64_t base = static_cast<int64_t>(blockIdx.x) * rows_per_cta; base < p.m;
        base += static_cast<int64_t>(gridDim.x) * rows_per_cta) {
@@ -46,7 +49,8 @@ __global__ void __launch_bounds__(256) row_reduce_kernel(const ReduceParams p) {
     const T* xr = x + row * p.ld;
     float acc = 0.f;
     if (live) {
-      for (int64_t col = static_cast<int64_t>(t) * EPV; col < p.n; col += static_cast<int64_t>(tpr) * EPV) {
+#pragma unroll 4
+      for (int64_t col = static_cast<int64_t>(t) * EPV; col < p.n; col += step) {
         float xv[EPV];
         if constexpr (VEC) {
           unpack16(ld_stream16(xr + col), xv);
@@ -57,15 +61,34 @@ __global__ void __launch_bounds__(256) row_reduce_kernel(const ReduceParams p) {
 #pragma unroll
           for (int j = 0; j < EPV; ++j) acc += xv[j];
         } else if (KIND == 1) {
+          if constexpr (VEC) {
+            // the vector in 16-byte loads too (it is re-read by every row, from L1/L2)
 #pragma unroll
-          for (int j = 0; j < EPV; ++j) acc += xv[j] * __ldg(vf + col + j);
+            for (int q = 0; q < EPV / 4; ++q) {
+              const float4 w = __ldg(reinterpret_cast<const float4*>(vf + col) + q);
+              acc += xv[4 * q] * w.x;
+              acc += xv[4 * q + 1] * w.y;
+              acc += xv[4 * q + 2] * w.z;
+              acc += xv[4 * q + 3] * w.w;
+            }
+          } else {
+            acc += xv[0] * __ldg(vf + col);
+          }
         } else {
+          if constexpr (VEC) {
+            float wv[EPV];
+            unpack16(__ldg(reinterpret_cast<const uint4*>(vt + col)), wv);
 #pragma unroll
-          for (int j = 0; j < EPV; ++j) acc += xv[j] * Elem<T>::load(vt + col + j);
+            for (int j = 0; j < EPV; ++j) acc += xv[j] * wv[j];
+          } else {
+            acc += xv[0] * Elem<T>::load(vt + col);
+          }
         }
       }
     }
-    acc = warp_sum(acc);
+    // Sum over the row's threads: an xor tree inside the (sub-)warp, then the warps in order.
+    for (int offset = (tpr < 32 ? tpr : 32) >> 1; offset > 0; offset >>= 1)
+      acc += __shfl_xor_sync(0xffffffffu, acc, offset);
     if (warps_per_row > 1) {
       if (lane == 0) red[row_in_cta * warps_per_row + warp_in_row] = acc;
       __syncthreads();
@@ -97,9 +120,10 @@ int run_row_reduce(int kind, ReduceParams p, cudaStream_t stream) {
   const DeviceInfo& dev = device_info();
   if (dev.sm_count == 0) return refuse(B200_E_DEVICE);
   const int kvec = Elem<T>::kVec;
-  const bool vec = (p.n % kvec == 0) && (p.ld % kvec == 0) && aligned(p.x, 16);
+  const bool vec = (p.n % kvec == 0) && (p.ld % kvec == 0) && aligned(p.x, 16) && (!p.v || aligned(p.v, 16));
   const int64_t units = vec ? p.n / kvec : p.n;
-  int tpr = 32;
+  // Threads per row: each thread gets about four 16-byte units, rows of up to 16 units share a warp.
+  int tpr = 4;
   while (tpr < 256 && static_cast<int64_t>(tpr) * 4 < units) tpr <<= 1;
   p.tpr = tpr;
   const int rows_per_cta = 256 / tpr;
@@ -115,21 +139,29 @@ int run_row_reduce(int kind, ReduceParams p, cudaStream_t stream) {
 // ---------------------------------------------------------------------------
 
 constexpr int kColThreads = 128;
-constexpr int kColTargetCtas = 592;  // four CTAs per SM of a 148-SM part
+constexpr int kColTargetCtas = 592;  // four CTAs per SM of a 148-SM part, for strips of 512 columns
 constexpr int kColMinRows = 64;
 
 struct ColPlan {
   int cols_per_thread;
+  int tpr_log2;  // threads side by side on a row (a power of two <= kColThreads); the rest of the CTA takes other rows
   int64_t col_tiles;
   int64_t chunks;
   int64_t rows_per_chunk;
 };
 
-ColPlan column_plan(int64_t m, int64_t n, bool vec4) {
+// `cpt`: columns per thread (1, 4, or 8 for 16-byte loads of bf16).
+ColPlan column_plan(int64_t m, int64_t n, int cpt) {
   ColPlan plan;
-  plan.cols_per_thread = vec4 ? 4 : 1;
-  plan.col_tiles = ceil_div(n, static_cast<int64_t>(kColThreads) * plan.cols_per_thread);
-  int64_t chunks = kColTargetCtas / (plan.col_tiles > 0 ? plan.col_tiles : 1);
+  plan.cols_per_thread = cpt;
+  const int64_t units = ceil_div(n, static_cast<int64_t>(plan.cols_per_thread));
+  plan.tpr_log2 = 0;
+  while ((1 << plan.tpr_log2) < kColThreads && (int64_t(1) << plan.tpr_log2) < units) ++plan.tpr_log2;
+  plan.col_tiles = ceil_div(units, int64_t(1) << plan.tpr_log2);
+  // Wider strips get fewer row chunks, so the partial sums (chunks x n floats) stay
+  // within kColTargetCtas x 512 floats whatever the strip width.
+  const int64_t strip = static_cast<int64_t>(cpt) << plan.tpr_log2;
+  int64_t chunks = kColTargetCtas * (strip > 512 ? 512 : strip) / strip / (plan.col_tiles > 0 ? plan.col_tiles : 1);
   const int64_t max_chunks = m / kColMinRows;
   if (chunks > max_chunks) chunks = max_chunks;
   if (chunks < 1) chunks = 1;
@@ -138,38 +170,65 @@ ColPlan column_plan(int64_t m, int64_t n, bool vec4) {
   return plan;
 }
 
-template <typename T, int CPT>
+// A CTA sums `rows_per_chunk` rows of one column tile. Narrow tiles (fewer columns
+// than the CTA has threads) are covered by several thread rows that take every
+// R-th row each; their partial sums are added in thread-row order at the end, so
+// the summation order is fixed.
+template <typename T, int CPT, bool MULTI>
 __global__ void __launch_bounds__(kColThreads) column_partial_kernel(const T* __restrict__ x, float* __restrict__ dst,
                                                                      int64_t m, int64_t n, int64_t ld,
-                                                                     int64_t rows_per_chunk) {
-  const int64_t col = (static_cast<int64_t>(blockIdx.x) * kColThreads + threadIdx.x) * CPT;
-  if (col >= n) return;
+                                                                     int64_t rows_per_chunk, int tpr_log2) {
+  __shared__ float red[MULTI ? kColThreads * CPT : 1];
+  // MULTI: the tile is narrower than the CTA, several thread rows share it (else one: plain row loop).
+  const int tpr = 1 << tpr_log2, thread_rows = MULTI ? (kColThreads >> tpr_log2) : 1;
+  const int tc = threadIdx.x & (tpr - 1), tr = threadIdx.x >> tpr_log2;
+  const int64_t col = (static_cast<int64_t>(blockIdx.x) * tpr + tc) * CPT;
+  const bool active = col < n;
   const int64_t r0 = static_cast<int64_t>(blockIdx.y) * rows_per_chunk;
   const int64_t r1 = (r0 + rows_per_chunk < m) ? r0 + rows_per_chunk : m;
   float acc[CPT];
 #pragma unroll
   for (int j = 0; j < CPT; ++j) acc[j] = 0.f;
-  const T* p = x + r0 * ld + col;
-#pragma unroll 4
-  for (int64_t r = r0; r < r1; ++r, p += ld) {
-    if (CPT == 4) {
-      if (sizeof(T) == 4) {
-        const float4 q = __ldg(reinterpret_cast<const float4*>(p));
-        acc[0] += q.x;
-        acc[1] += q.y;
-        acc[2] += q.z;
-        acc[3] += q.w;
+  if (active) {
+    const T* p = x + (r0 + tr) * ld + col;
+    const int64_t stride = static_cast<int64_t>(thread_rows) * ld;
+#pragma unroll 8
+    for (int64_t r = r0 + tr; r < r1; r += thread_rows, p += stride) {
+      if (CPT == 8) {
+        float v[8];
+        unpack16(__ldg(reinterpret_cast<const uint4*>(p)), v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += v[j];
+      } else if (CPT == 4) {
+        if (sizeof(T) == 4) {
+          const float4 q = __ldg(reinterpret_cast<const float4*>(p));
+          acc[0] += q.x;
+          acc[1] += q.y;
+          acc[2] += q.z;
+          acc[3] += q.w;
+        } else {
+          const uint2 q = __ldg(reinterpret_cast<const uint2*>(p));
+          acc[0] += __uint_as_float(q.x << 16);
+          acc[1] += __uint_as_float(q.x & 0xffff0000u);
+          acc[2] += __uint_as_float(q.y << 16);
+          acc[3] += __uint_as_float(q.y & 0xffff0000u);
+        }
       } else {
-        const uint2 q = __ldg(reinterpret_cast<const uint2*>(p));
-        acc[0] += __uint_as_float(q.x << 16);
-        acc[1] += __uint_as_float(q.x & 0xffff0000u);
-        acc[2] += __uint_as_float(q.y << 16);
-        acc[3] += __uint_as_float(q.y & 0xffff0000u);
+        acc[0] += Elem<T>::load(p);
       }
-    } else {
-      acc[0] += Elem<T>::load(p);
     }
   }
+  if (MULTI) {
+#pragma unroll
+    for (int j = 0; j < CPT; ++j) red[threadIdx.x * CPT + j] = acc[j];
+    __syncthreads();
+    if (tr != 0) return;
+    for (int other = 1; other < thread_rows; ++other) {
+#pragma unroll
+      for (int j = 0; j < CPT; ++j) acc[j] += red[(other * tpr + tc) * CPT + j];
+    }
+  }
+  if (!active) return;
   float* d = dst + static_cast<int64_t>(blockIdx.y) * n + col;
 #pragma unroll
   for (int j = 0; j < CPT; ++j) d[j] = acc[j];
@@ -184,15 +243,17 @@ __global__ void column_final_kernel(const float* __restrict__ partial, float* __
   out[col] = acc;
 }
 
-bool column_vec4(int32_t dtype, const void* x, int64_t n, int64_t ld) {
+// Columns per thread: 8 (bf16) or 4 as one 16-byte load, 4 bf16 as an 8-byte load, else 1.
+int column_cpt(int32_t dtype, const void* x, int64_t n, int64_t ld) {
+  if (dtype == B200_BF16 && n % 8 == 0 && ld % 8 == 0 && aligned(x, 16)) return 8;
   const size_t bytes = 4 * dtype_size(dtype);
-  return n % 4 == 0 && ld % 4 == 0 && aligned(x, bytes);
+  return (n % 4 == 0 && ld % 4 == 0 && aligned(x, bytes)) ? 4 : 1;
 }
 
 int column_sum_impl(int32_t dtype, const void* x, float* out, int64_t m, int64_t n, int64_t ld, void* workspace,
                     size_t workspace_bytes, cudaStream_t stream) {
-  const bool vec4 = column_vec4(dtype, x, n, ld);
-  const ColPlan plan = column_plan(m, n, vec4);
+  const int cpt = column_cpt(dtype, x, n, ld);
+  const ColPlan plan = column_plan(m, n, cpt);
   float* stage1 = out;
   if (plan.chunks > 1) {
     const size_t need = static_cast<size_t>(plan.chunks) * n * sizeof(float);
@@ -201,20 +262,27 @@ int column_sum_impl(int32_t dtype, const void* x, float* out, int64_t m, int64_t
     stage1 = static_cast<float*>(workspace);
   }
   const dim3 grid(static_cast<unsigned>(plan.col_tiles), static_cast<unsigned>(plan.chunks));
+  const bool multi = plan.tpr_log2 < 7;  // fewer column threads than the CTA has
+  auto launch = [&](auto kernel_multi, auto kernel_single, auto xs) {
+    if (multi)
+      kernel_multi<<<grid, kColThreads, 0, stream>>>(xs, stage1, m, n, ld, plan.rows_per_chunk, plan.tpr_log2);
+    else
+      kernel_single<<<grid, kColThreads, 0, stream>>>(xs, stage1, m, n, ld, plan.rows_per_chunk, plan.tpr_log2);
+  };
   if (dtype == B200_F32) {
     const float* xs = static_cast<const float*>(x);
-    if (vec4)
-      column_partial_kernel<float, 4><<<grid, kColThreads, 0, stream>>>(xs, stage1, m, n, ld, plan.rows_per_chunk);
+    if (cpt == 4)
+      launch(column_partial_kernel<float, 4, true>, column_partial_kernel<float, 4, false>, xs);
     else
-      column_partial_kernel<float, 1><<<grid, kColThreads, 0, stream>>>(xs, stage1, m, n, ld, plan.rows_per_chunk);
+      launch(column_partial_kernel<float, 1, true>, column_partial_kernel<float, 1, false>, xs);
   } else {
     const __nv_bfloat16* xs = static_cast<const __nv_bfloat16*>(x);
-    if (vec4)
-      column_partial_kernel<__nv_bfloat16, 4>
-          <<<grid, kColThreads, 0, stream>>>(xs, stage1, m, n, ld, plan.rows_per_chunk);
+    if (cpt == 8)
+      launch(column_partial_kernel<__nv_bfloat16, 8, true>, column_partial_kernel<__nv_bfloat16, 8, false>, xs);
+    else if (cpt == 4)
+      launch(column_partial_kernel<__nv_bfloat16, 4, true>, column_partial_kernel<__nv_bfloat16, 4, false>, xs);
     else
-      column_partial_kernel<__nv_bfloat16, 1>
-          <<<grid, kColThreads, 0, stream>>>(xs, stage1, m, n, ld, plan.rows_per_chunk);
+      launch(column_partial_kernel<__nv_bfloat16, 1, true>, column_partial_kernel<__nv_bfloat16, 1, false>, xs);
   }
   if (plan.chunks > 1) {
     const unsigned blocks = static_cast<unsigned>(ceil_div(n, 256));
@@ -226,9 +294,12 @@ int column_sum_impl(int32_t dtype, const void* x, float* out, int64_t m, int64_t
 
 size_t column_sum_workspace(int64_t m, int64_t n) {
   if (m <= 0 || n <= 0) return 0;
-  // The vectorised plan has the fewest column tiles, hence the most chunks.
-  const ColPlan a = column_plan(m, n, true), b = column_plan(m, n, false);
-  const int64_t chunks = a.chunks > b.chunks ? a.chunks : b.chunks;
+  // Whichever vector width the operand's alignment allows at call time.
+  int64_t chunks = 1;
+  for (int cpt : {1, 4, 8}) {
+    const ColPlan plan = column_plan(m, n, cpt);
+    if (plan.chunks > chunks) chunks = plan.chunks;
+  }
   return chunks > 1 ? static_cast<size_t>(chunks) * n * sizeof(float) : 0;
 }
 
