@@ -117,6 +117,162 @@ __global__ void __launch_bounds__(256) pack_rows_kernel(const PackParams p) {
   }
 }
 
+// ---------------------------------------------------------------------------
+// Transposing packs through shared memory. A CTA moves a tile of 32 source rows by
+// 512 bytes: the read phase takes 16-byte vectors along the source rows (a warp
+// reads one row's 512 bytes), the write phase 16-byte vectors along the source
+// columns, which is the direction the destination is contiguous in. UNIT is the
+// size of what is transposed: one element, or a bf16 K pair (4 bytes) for VNNI.
+// Shared rows are padded by one word, so the column gathers of the write phase are
+// conflict-free; the row stores of the read phase take four wavefronts each, which
+// shared memory has to spare next to an HBM stream.
+//   PACK_A_BLOCKED_T  src [K, M]: dst[m/32][k/32][m%32][k%32]           (elements)
+//   PACK_B_BLOCKED_T  src [N, K]: dst[n/32][k/32][k%32][n%32]           (elements)
+//   PACK_B_VNNI_T     src [N, K]: dst[n/32][c][n%32] pairs, c = k/2     (panel = 32)
+//   PACK_B_VNNI_PANELS_T          dst[n/P][c][n%P]  pairs
+//   UNPACK_B_VNNI_PANELS_TO_NK    src[n/P][c][n%P] pairs -> dst[n][c]   (P >= 64)
+// ---------------------------------------------------------------------------
+template <typename T, int UNIT, int KIND>
+__global__ void __launch_bounds__(256) pack_transpose_kernel(const PackParams p) {
+  constexpr int kUnitsPerRow = 512 / UNIT;      // tile columns, in units
+  constexpr int kVecUnits = 16 / UNIT;          // units per 16-byte vector
+  constexpr int kElemsPerUnit = UNIT / static_cast<int>(sizeof(T));
+  constexpr int kPitchWords = 128 + 1;
+  constexpr int kRunVectors = 32 * UNIT / 16;   // vectors in a destination run of 32 units
+  __shared__ uint32_t tile[32 * kPitchWords];
+  const T* __restrict__ src = static_cast<const T*>(p.src);
+  uint8_t* __restrict__ dst = static_cast<uint8_t*>(p.dst);
+  const int64_t row0 = static_cast<int64_t>(blockIdx.y) * 32;            // first source row of the tile
+  const int64_t unit0 = static_cast<int64_t>(blockIdx.x) * kUnitsPerRow;  // first source column, in units
+
+  // ---- read: 32 rows x 32 vectors
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int v = threadIdx.x + 256 * i;
+    const int r = v >> 5, cv = (v & 31) * kVecUnits;
+    const int64_t row = row0 + r;
+    const int64_t col = (unit0 + cv) * kElemsPerUnit;  // first element of the vector
+    constexpr int kVecElems = 16 / static_cast<int>(sizeof(T));
+    uint4 q = make_uint4(0, 0, 0, 0);
+    if (KIND == B200_UNPACK_B_VNNI_PANELS_TO_NK) {
+      // source [panel z][pair row][p.panel columns] of K pairs, all of it valid and 16-byte aligned
+      if (row < (p.cols_pad >> 1) && unit0 + cv < p.panel)
+        q = ld_stream16(reinterpret_cast<const uint32_t*>(p.src) +
+                        (static_cast<int64_t>(blockIdx.z) * (p.cols_pad >> 1) + row) * p.panel + unit0 + cv);
+    } else if (row < p.rows && col < p.cols) {
+      const T* at = src + row * p.ld + col;
+      if (col + kVecElems <= p.cols && (reinterpret_cast<uintptr_t>(at) & 15) == 0) {
+        q = ld_stream16(at);
+      } else {
+        T e[kVecElems];
+#pragma unroll
+        for (int j = 0; j < kVecElems; ++j) {
+          if (col + j < p.cols) {
+            e[j] = at[j];
+          } else {
+            memset(&e[j], 0, sizeof(T));
+          }
+        }
+        memcpy(&q, e, 16);
+      }
+    }
+    uint32_t* w = &tile[r * kPitchWords + (cv * UNIT) / 4];
+    w[0] = q.x;
+    w[1] = q.y;
+    w[2] = q.z;
+    w[3] = q.w;
+  }
+  __syncthreads();
+
+  // ---- write: for every source column a run of 32 units, 16 bytes per thread
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int w = threadIdx.x + 256 * i;
+    const int g = w % kRunVectors, c = w / kRunVectors;
+    const int64_t unit = unit0 + c;  // source column of this run, in units
+    uint32_t out[4];
+    if (UNIT == 4) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) out[k] = tile[(g * 4 + k) * kPitchWords + c];
+    } else {
+      const uint16_t* halves = reinterpret_cast<const uint16_t*>(tile);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t lo = halves[(g * 8 + 2 * k) * kPitchWords * 2 + c];
+        const uint32_t hi = halves[(g * 8 + 2 * k + 1) * kPitchWords * 2 + c];
+        out[k] = lo | (hi << 16);
+      }
+    }
+    int64_t offset;  // destination offset of the run's first unit, in units
+    bool inside;
+    if (KIND == B200_PACK_A_BLOCKED_T) {
+      // source rows are k, columns m: row0 / 32 is the K block
+      const int64_t kblocks = p.rows_pad >> 5;
+      inside = unit < p.cols_pad;
+      offset = (((unit >> 5) * kblocks + (row0 >> 5)) << 10) + ((unit & 31) << 5);
+    } else if (KIND == B200_PACK_B_BLOCKED_T) {
+      // source rows are n, columns k
+      const int64_t kblocks = p.cols_pad >> 5;
+      inside = unit < p.cols_pad;
+      offset = (((row0 >> 5) * kblocks + (unit >> 5)) << 10) + ((unit & 31) << 5);
+    } else if (KIND == B200_UNPACK_B_VNNI_PANELS_TO_NK) {
+      // source rows are pairs, columns the panel's n: dst32[z * panel + n][pair]
+      inside = unit < p.panel && row0 + g * kVecUnits < (p.cols_pad >> 1);  // the last tile of pairs may be short
+      offset = (static_cast<int64_t>(blockIdx.z) * p.panel + unit) * (p.cols_pad >> 1) + row0;
+    } else {
+      // K pairs: source rows are n, columns pairs; panels of p.panel rows (32 for the blocked VNNI layout)
+      const int64_t pairs = p.cols_pad >> 1;
+      const int64_t panel = KIND == B200_PACK_B_VNNI_T ? 32 : p.panel;
+      inside = unit < pairs;
+      offset = ((row0 / panel) * pairs + unit) * panel + (row0 % panel);
+    }
+    if (inside)
+      st_stream16(dst + (offset + g * kVecUnits) * UNIT, make_uint4(out[0], out[1], out[2], out[3]));
+  }
+}
+
+// [K, N] -> VNNI blocks dst[n/32][c][n%32][2], c = k/2: rows 2c and 2c+1 interleaved
+// element by element. A thread takes 8 columns of both rows (16 bytes each) and
+// writes 32 contiguous bytes; four lanes fill one 128-byte run of a block.
+__global__ void __launch_bounds__(256) pack_vnni_rows_kernel(const PackParams p) {
+  const __nv_bfloat16* __restrict__ src = static_cast<const __nv_bfloat16*>(p.src);
+  uint8_t* __restrict__ dst = static_cast<uint8_t*>(p.dst);
+  const int64_t pairs = p.rows_pad >> 1, groups = p.cols_pad >> 3;  // source rows are k, columns n
+  const int64_t total = pairs * groups;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t u = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; u < total; u += stride) {
+    const int64_t c = u / groups, n0 = (u - c * groups) << 3;
+    uint4 rows[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int64_t k = 2 * c + h;
+      rows[h] = make_uint4(0, 0, 0, 0);
+      if (k < p.rows && n0 < p.cols) {
+        const __nv_bfloat16* at = src + k * p.ld + n0;
+        if (n0 + 8 <= p.cols && (reinterpret_cast<uintptr_t>(at) & 15) == 0) {
+          rows[h] = ld_stream16(at);
+        } else {
+          __nv_bfloat16 e[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) e[j] = (n0 + j < p.cols) ? at[j] : __float2bfloat16_rn(0.f);
+          memcpy(&rows[h], e, 16);
+        }
+      }
+    }
+    const uint32_t a[4] = {rows[0].x, rows[0].y, rows[0].z, rows[0].w};
+    const uint32_t b[4] = {rows[1].x, rows[1].y, rows[1].z, rows[1].w};
+    uint32_t out[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      out[2 * j] = __byte_perm(a[j], b[j], 0x5410);      // (row 2c, row 2c+1) of column 2j
+      out[2 * j + 1] = __byte_perm(a[j], b[j], 0x7632);  // of column 2j + 1
+    }
+    uint8_t* at = dst + (((n0 >> 5) * pairs + c) * 64 + (n0 & 31) * 2) * 2;
+    st_stream16(at, make_uint4(out[0], out[1], out[2], out[3]));
+    st_stream16(at + 16, make_uint4(out[4], out[5], out[6], out[7]));
+  }
+}
+
 // VNNI -> [Np, Kp] (K contiguous), as a transpose of 32-bit K pairs:
 //   blocks: src32[j][kb][r][nn]  -> dst32[32j+nn][16kb+r]
 //   panels: src32[q][c][nn]      -> dst32[qP+nn][c]
@@ -236,6 +392,17 @@ int launch_pack(const PackParams& p, cudaStream_t stream) {
   return launched();
 }
 
+// Grid of the transposing packs: source rows in blocks of 32, source columns (in
+// units) in tiles of 512 bytes. Falls back to the gather kernel beyond the grid limits.
+template <typename T, int UNIT, int KIND>
+int launch_transpose(const PackParams& p, int64_t rows_pad, int64_t units_pad, cudaStream_t stream) {
+  const int64_t tiles_r = ceil_div(rows_pad, 32), tiles_c = ceil_div(units_pad, 512 / UNIT);
+  if (tiles_r > 65535 || tiles_c > 0x7fffffff) return launch_pack<T, KIND, false>(p, stream);
+  const dim3 grid(static_cast<unsigned>(tiles_c), static_cast<unsigned>(tiles_r));
+  pack_transpose_kernel<T, UNIT, KIND><<<grid, 256, 0, stream>>>(p);
+  return launched();
+}
+
 template <typename T>
 int run_pack(int kind, const PackParams& p, cudaStream_t stream) {
   constexpr int W = 16 / sizeof(T);
@@ -248,17 +415,30 @@ int run_pack(int kind, const PackParams& p, cudaStream_t stream) {
       if (dst16) return launch_pack<T, B200_PACK_A_BLOCKED, true>(p, stream);
       return launch_pack<T, B200_PACK_A_BLOCKED, false>(p, stream);
     case B200_PACK_A_BLOCKED_T:
+      if (dst16) return launch_transpose<T, sizeof(T), B200_PACK_A_BLOCKED_T>(p, p.rows_pad, p.cols_pad, stream);
       return launch_pack<T, B200_PACK_A_BLOCKED_T, false>(p, stream);
     case B200_PACK_B_BLOCKED:  // 32 n adjacent in source rows
       if (dst16) return launch_pack<T, B200_PACK_B_BLOCKED, true>(p, stream);
       return launch_pack<T, B200_PACK_B_BLOCKED, false>(p, stream);
     case B200_PACK_B_BLOCKED_T:
+      if (dst16) return launch_transpose<T, sizeof(T), B200_PACK_B_BLOCKED_T>(p, p.rows_pad, p.cols_pad, stream);
       return launch_pack<T, B200_PACK_B_BLOCKED_T, false>(p, stream);
     case B200_PACK_B_VNNI:
+      if (dst16 && sizeof(T) == 2) {
+        const int64_t units = (p.rows_pad >> 1) * (p.cols_pad >> 3);
+        const int64_t wanted = ceil_div(units, 256), resident = static_cast<int64_t>(device_info().sm_count) * 8;
+        pack_vnni_rows_kernel<<<static_cast<unsigned>(wanted < resident ? wanted : resident), 256, 0, stream>>>(p);
+        return launched();
+      }
       return launch_pack<T, B200_PACK_B_VNNI, false>(p, stream);
     case B200_PACK_B_VNNI_T:
+      // K pairs as 4-byte units need an even row pitch and a 4-byte aligned source
+      if (dst16 && sizeof(T) == 2 && p.ld % 2 == 0 && aligned(p.src, 4))
+        return launch_transpose<T, 4, B200_PACK_B_VNNI_T>(p, p.rows_pad, p.cols_pad >> 1, stream);
       return launch_pack<T, B200_PACK_B_VNNI_T, false>(p, stream);
     default:
+      if (dst16 && sizeof(T) == 2 && p.ld % 2 == 0 && aligned(p.src, 4))
+        return launch_transpose<T, 4, B200_PACK_B_VNNI_PANELS_T>(p, p.rows_pad, p.cols_pad >> 1, stream);
       return launch_pack<T, B200_PACK_B_VNNI_PANELS_T, false>(p, stream);
   }
 }
@@ -301,6 +481,20 @@ extern "C" int b200_pack(int32_t kind, int32_t dtype, const void* src, int64_t r
     const int64_t pairs = cols_pad / 2;
     const dim3 grid(static_cast<unsigned>(ceil_div(pairs, 32)), static_cast<unsigned>(ceil_div(rows_pad, 32)));
     if (grid.y > 65535) return refuse(B200_E_SHAPE);
+    if (panels && panel >= 64 && panel % 4 == 0 && pairs % 4 == 0 && aligned(src, 16) && aligned(dst, 16) &&
+        rows_pad / panel <= 65535 && ceil_div(pairs, 32) <= 65535) {
+      // wide panels: the tiled transpose (16-byte accesses on both sides)
+      PackParams p{};
+      p.src = src;
+      p.dst = dst;
+      p.rows_pad = rows_pad;
+      p.cols_pad = cols_pad;
+      p.panel = panel;
+      const dim3 tiles(static_cast<unsigned>(ceil_div(panel, 128)), static_cast<unsigned>(ceil_div(pairs, 32)),
+                       static_cast<unsigned>(rows_pad / panel));
+      pack_transpose_kernel<__nv_bfloat16, 4, B200_UNPACK_B_VNNI_PANELS_TO_NK><<<tiles, 256, 0, s>>>(p);
+      return launched();
+    }
     if (panels)
       unpack_vnni_kernel<true><<<grid, 256, 0, s>>>(static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst),
                                                     rows_pad, pairs, panel);
