@@ -298,9 +298,18 @@ class F32Matmul(Workload):
         self.c_pinned = torch.empty(self.SIZE, self.SIZE).pin_memory()
         self.a_stage, self.b_stage = torch.empty_like(self.a[0]), torch.empty_like(self.b[0])
 
+        # The call is three short kernels (two operand splits and the GEMM): replayed as
+        # one CUDA graph per operand pair, which takes the host out of the timed loop.
+        from helion_mlir_backend import graphed
+
+        self.calls = [graphed(lambda a, b: ops.matmul(a, b, block_sizes=(64, 64, 64)), a, b)
+                      for a, b in zip(self.a, self.b)]
+        self.graph_launches = 0
+
     def step(self, index: int) -> torch.Tensor:
-        i = index % self.SETS
-        return self.ops.matmul(self.a[i], self.b[i], block_sizes=(64, 64, 64))
+        call = self.calls[index % self.SETS]
+        self.graph_launches += call.kernels  # replays do not pass the library's launch counter
+        return call()
 
     def e2e_step(self, index: int) -> tuple[int, int]:
         self.a_stage.copy_(self.a_pinned, non_blocking=True)
@@ -313,6 +322,7 @@ class F32Matmul(Workload):
 
     def config(self) -> dict[str, object]:
         return {"workload": self.name, "block_sizes": [64, 64, 64], "sharding": "replicas only",
+                "launch": "one CUDA graph replay per call (split A, split B, GEMM)",
                 "l2": f"{self.SETS} rotating operand pairs (101 MB) plus outputs > 126 MB L2"}
 
     def cpu_sample(self, threads: int) -> tuple[float, str]:
@@ -555,13 +565,14 @@ def main() -> None:
     barrier()
     launches_before = native.counters()["launches"]
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    graph_before = getattr(workload, "graph_launches", 0)
     barrier()
     start.record()
     for i in range(args.steps):
         workload.step(i)
     stop.record()
     barrier()
-    launches = native.counters()["launches"] - launches_before
+    launches = native.counters()["launches"] - launches_before + getattr(workload, "graph_launches", 0) - graph_before
     device_ms = start.elapsed_time(stop)
     clocks = sampler.stop() if rank == 0 else {}
 

@@ -15,6 +15,8 @@ from .api import lower_mlir as lower_mlir
 from .call_trace import CallExplanation as CallExplanation
 from .call_trace import explain as explain
 from .driver import prepared_call as prepared_call
+from .graphs import GraphedCall as GraphedCall
+from .graphs import graphed as graphed
 from .errors import MLIRBackendError as MLIRBackendError
 from .errors import UnsupportedOperationError as UnsupportedOperationError
 from .inject import install as install
@@ -25,12 +27,14 @@ from .output_pool import set_output_pool as set_output_pool
 
 __all__ = [
     "CallExplanation",
+    "GraphedCall",
     "InlineMLIRHint",
     "MLIRBackendError",
     "UnsupportedOperationError",
     "compile_mlir",
     "explain",
     "generate_mlir",
+    "graphed",
     "inline_mlir",
     "install",
     "lower_mlir",

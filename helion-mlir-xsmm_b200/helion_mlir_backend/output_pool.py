@@ -118,12 +118,15 @@ _misses = 0
 
 
 def _plain_dispatch() -> bool:
-    """No torch-function or dispatch mode, no transform and no trace."""
+    """No torch-function or dispatch mode, no transform, no trace and no CUDA graph
+    capture (a captured allocation must come from torch's capture-aware allocator:
+    the pool would query events and may call cudaMalloc, neither of which a capture allows)."""
     return not (
         torch._C._is_torch_function_mode_enabled()
         or torch._C._len_torch_dispatch_stack()
         or torch._C._functorch.peek_interpreter_stack() is not None
         or torch.jit.is_tracing()
+        or torch.cuda.is_current_stream_capturing()
     )
 
 
