@@ -149,6 +149,50 @@ __device__ __forceinline__ float fast_erf(float x) {
   return copysignf(fmaf(-poly, e, 1.f), x);
 }
 
+// Two f32 values in one 64-bit register for the packed FP32 instructions of sm_100
+// (fma / mul / add .f32x2: one issue slot for two results).
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// GELU (erf form) of two values at once: the arithmetic of fast_erf above, step for
+// step, with every multiply-add done on the pair. Same results as the scalar form.
+__device__ __forceinline__ void gelu_erf_pair(float& a, float& b) {
+  const uint64_t x = pack_f32x2(a, b);
+  const uint64_t s = mul_f32x2(x, pack_f32x2(0.70710678118654752f, 0.70710678118654752f));
+  const uint64_t z = s & 0x7fffffff7fffffffull;
+  float d0, d1;
+  unpack_f32x2(fma_f32x2(pack_f32x2(0.3275911f, 0.3275911f), z, pack_f32x2(1.f, 1.f)), d0, d1);
+  const uint64_t t = pack_f32x2(fast_rcp(d0), fast_rcp(d1));
+  uint64_t poly = fma_f32x2(pack_f32x2(1.061405429f, 1.061405429f), t, pack_f32x2(-1.453152027f, -1.453152027f));
+  poly = fma_f32x2(poly, t, pack_f32x2(1.421413741f, 1.421413741f));
+  poly = fma_f32x2(poly, t, pack_f32x2(-0.284496736f, -0.284496736f));
+  poly = fma_f32x2(poly, t, pack_f32x2(0.254829592f, 0.254829592f));
+  poly = mul_f32x2(poly, t);
+  float q0, q1;
+  unpack_f32x2(mul_f32x2(mul_f32x2(z, z), pack_f32x2(-1.4426950408889634f, -1.4426950408889634f)), q0, q1);
+  const uint64_t e = pack_f32x2(fast_exp2(q0), fast_exp2(q1));
+  // 1 - poly * e, with the sign of s
+  uint64_t erf = fma_f32x2(poly ^ 0x8000000080000000ull, e, pack_f32x2(1.f, 1.f));
+  erf = (erf & 0x7fffffff7fffffffull) | (s & 0x8000000080000000ull);
+  const uint64_t half = mul_f32x2(x, pack_f32x2(0.5f, 0.5f));
+  unpack_f32x2(fma_f32x2(half, erf, half), a, b);
+}
+
 __device__ __forceinline__ float warp_fmax(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
@@ -163,15 +207,17 @@ __device__ __forceinline__ float apply_act(int act, float x, float alpha) {
     case B200_ACT_GELU_ERF:
       return 0.5f * x * (1.f + fast_erf(x * 0.70710678118654752f));
     case B200_ACT_GELU_TANH: {
-      const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-      return 0.5f * x * (1.f + tanhf(u));
+      // 0.5 x (1 + tanh(u)) = x * sigmoid(2u)
+      const float u2 = 1.5957691216057308f * (x + 0.044715f * x * x * x);
+      return x * fast_rcp(1.f + fast_exp2(u2 * -1.4426950408889634f));
     }
     case B200_ACT_SIGMOID:
-      return 1.f / (1.f + __expf(-x));
+      return fast_rcp(1.f + fast_exp2(x * -1.4426950408889634f));
     case B200_ACT_TANH:
-      return tanhf(x);
+      // 1 - 2 / (1 + e^(2x)): exact limits at both ends, absolute error about 1e-7
+      return 1.f - 2.f * fast_rcp(1.f + fast_exp2(x * 2.8853900817779268f));
     case B200_ACT_SILU:
-      return x / (1.f + __expf(-x));
+      return x * fast_rcp(1.f + fast_exp2(x * -1.4426950408889634f));
     case B200_ACT_LEAKY_RELU:
       return x > 0.f ? x : x * alpha;
     default:

@@ -149,7 +149,7 @@ __device__ __forceinline__ void activate32(int act, float alpha, float (&v)[32])
       break;
     case B200_ACT_GELU_ERF:
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = apply_act(B200_ACT_GELU_ERF, v[j], alpha);
+      for (int j = 0; j < 32; j += 2) gelu_erf_pair(v[j], v[j + 1]);
       break;
     case B200_ACT_GELU_TANH:
 #pragma unroll
