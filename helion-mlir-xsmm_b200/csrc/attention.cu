@@ -7,8 +7,9 @@
 //   warps 4-7  softmax group 1: the odd key blocks.   (TMEM lane r) in both groups.
 //              Per block a thread loads its 128 scores from the group's TMEM score
 //              buffer, keeps the group's running maximum and sum of its row, writes
-//              P = exp2(score * scale * log2e - max) as bf16 into the group's shared
-//              memory tile in the tensor core's K-major swizzled layout, and rescales
+//              P = exp2(score * scale * log2e - max) as bf16 pairs back into tensor
+//              memory over the scores it has just read (tcgen05.st; the second
+//              product takes its A operand from there), and rescales
 //              the group's output accumulator only when some row's maximum grew by
 //              more than 2^8 (the reference body's _RESCALE_THRESHOLD idea: a stale
 //              maximum only scales numerator and denominator alike). The two groups
@@ -18,11 +19,12 @@
 //              At the end the groups' (maximum, sum, accumulator) are merged:
 //              out = (O0 w0 + O1 w1) / (sum0 w0 + sum1 w1), w = 2^(max - common max).
 //   warp 8     TMA producers: lane 0 loads Q once and the K blocks, lane 1 the V blocks
-//   warp 9     MMA issuer (one lane): S_j = Q K_j^T into score buffer j % 2, issued
-//              two blocks ahead (as soon as the group has S_{j-2} in registers);
-//              O_{j%2} += P_j V_j when the group has written P_j.
-// TMEM: columns [0,128) and [128,256) scores, [256, 256+D) and [256+D, 256+2D) the
-// two output accumulators.
+//   warp 9     MMA issuer (one lane): O_{j%2} += P_j V_j when the group has written P_j
+//              (A from tensor memory, B = V from shared memory), then S_{j+2} = Q K_{j+2}^T
+//              into the same score buffer (in issue order after the P V that reads it).
+// TMEM: columns [0,128) and [128,256) scores of the two groups, whose first 64 columns
+// are reused for P (two bf16 per column); [256, 256+D) and [256+D, 256+2D) the two
+// output accumulators. Shared memory holds only Q and the K / V stages.
 //
 // Keys past the end of the sequence arrive as zeros from TMA and are masked to
 // -inf before the maximum; query rows past the end are computed and not stored.
@@ -59,7 +61,7 @@ struct __align__(8) AttnBarriers {
   uint64_t q_full;
   uint64_t k_full[kMaxStages], k_empty[kMaxStages];
   uint64_t v_full[kMaxStages], v_empty[kMaxStages];
-  uint64_t s_full[2], s_empty[2];  // per score buffer = per group
+  uint64_t s_full[2];              // per score buffer = per group
   uint64_t p_full[2], pv_done[2];  // per group
   uint64_t merge[4];               // the two warps of a TMEM lane quarter meet here at the end
   uint32_t tmem_base;
@@ -76,17 +78,16 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                      const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
   constexpr int kChunks = D / 64;                       // 64-element column chunks of a D-wide tile
-  constexpr int kStages = D == 64 ? 4 : 2;              // what fits beside Q and P in shared memory
+  constexpr int kStages = D == 64 ? 4 : 3;              // K and V stages beside Q in shared memory
   constexpr uint32_t kTileBytes = kChunks * 16384;      // 128 rows x D bf16
   constexpr uint32_t kVHalfBytes = kChunks * 8192;      // 64 keys x D bf16 (MN-major chunks of 8 KiB)
-  constexpr uint32_t kPBytes = 32768;                   // 128 rows x 128 keys bf16, two K-major chunks
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t q_smem = smem_base;
   const uint32_t k_smem = q_smem + kTileBytes;
   const uint32_t v_smem = k_smem + kStages * kTileBytes;
-  const uint32_t p_smem = v_smem + kStages * kTileBytes;  // one tile per group
-  AttnBarriers* bars = reinterpret_cast<AttnBarriers*>(smem_raw + (p_smem + 2 * kPBytes - smem_u32(smem_raw)));
+  const uint32_t end_smem = v_smem + kStages * kTileBytes;
+  AttnBarriers* bars = reinterpret_cast<AttnBarriers*>(smem_raw + (end_smem - smem_u32(smem_raw)));
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -104,7 +105,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     }
     for (int g = 0; g < 2; ++g) {
       mbar_init(smem_u32(&bars->s_full[g]), 1);
-      mbar_init(smem_u32(&bars->s_empty[g]), kGroupWarps);
       mbar_init(smem_u32(&bars->p_full[g]), kGroupWarps);
       mbar_init(smem_u32(&bars->pv_done[g]), 1);
     }
@@ -177,12 +177,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       tc_fence_after();
       const uint64_t q_desc = make_desc(q_smem, 1u, hi);
       // S_j = Q K_j^T into score buffer j % 2: both operands K-major, D/16 MMAs of K = 16.
-      // The buffer is free once its group holds S_{j-2} in registers.
       auto issue_scores = [&](int j) -> bool {
         const uint32_t st = j % kStages, g = j & 1;
         if (!mbar_wait(smem_u32(&bars->k_full[st]), (j / kStages) & 1, abort_flag, p.status, kErrAttnMma)) return false;
-        if (!mbar_wait(smem_u32(&bars->s_empty[g]), ((j >> 1) & 1) ^ 1, abort_flag, p.status, kErrAttnMma))
-          return false;
         tc_fence_after();
         const uint64_t k_desc = make_desc(k_smem + st * kTileBytes, 1u, hi);
         uint32_t accumulate = 0;
@@ -202,11 +199,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       if (ok && nb > 0) ok = issue_scores(0);
       if (ok && nb > 1) ok = issue_scores(1);
       for (int j = 0; j < nb && ok; ++j) {
-        if (j + 2 < nb) {
-          ok = issue_scores(j + 2);
-          if (!ok) break;
-        }
-        // O_g += P_j V_j: P K-major (two 64-key chunks), V MN-major (64-key halves of D/64 chunks).
+        // O_g += P_j V_j: P from tensor memory (8 columns = 16 keys per MMA), V MN-major
+        // in shared memory (64-key halves of D/64 chunks).
         const uint32_t st = j % kStages, g = j & 1;
         ok = mbar_wait(smem_u32(&bars->v_full[st]), (j / kStages) & 1, abort_flag, p.status, kErrAttnMma);
         if (ok) ok = mbar_wait(smem_u32(&bars->p_full[g]), (j >> 1) & 1, abort_flag, p.status, kErrAttnMma);
@@ -215,17 +209,19 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         uint32_t accumulate = j > 1 ? 1u : 0u;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          const uint64_t p_desc = make_desc(p_smem + g * kPBytes + h * 16384, 1u, hi);
           const uint64_t v_desc = make_desc(v_smem + st * kTileBytes + h * kVHalfBytes, 8192u >> 4, hi);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            umma_bf16<1>(tmem_base + kOutCol + g * D, p_desc + static_cast<uint64_t>((i * 32) >> 4),
+            umma_bf16_ts(tmem_base + kOutCol + g * D, tmem_base + g * kScoreCols + (h * 4 + i) * 8,
                          v_desc + static_cast<uint64_t>((i * 2048) >> 4), p.idesc_pv, accumulate);
             accumulate = 1;
           }
         }
         umma_commit<1>(smem_u32(&bars->v_empty[st]));
         umma_commit<1>(smem_u32(&bars->pv_done[g]));
+        // The next scores of this group go where P_j lies: issued after the P V that reads
+        // it, and the tensor core runs what one thread issues in order.
+        if (j + 2 < nb) ok = issue_scores(j + 2);
       }
     }
     __syncwarp();
@@ -239,9 +235,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     float top = -1.0e30f, total = 0.f;
     const bool negative = p.scale_log2 < 0.f;  // then the largest scaled score is the smallest raw one
     bool ok = true;
-    const uint32_t p_row = p_smem + g * kPBytes + row * 128;
-    const uint32_t swz = static_cast<uint32_t>(row & 7);
-    const uint32_t s_full = smem_u32(&bars->s_full[g]), s_empty = smem_u32(&bars->s_empty[g]);
+    const uint32_t s_full = smem_u32(&bars->s_full[g]);
     const uint32_t p_full = smem_u32(&bars->p_full[g]), pv_done = smem_u32(&bars->pv_done[g]);
     int mine = 0;  // blocks this group has taken
     for (int j = g; j < nb && ok; j += 2, ++mine) {
@@ -258,10 +252,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           tmem_ld_32x32(score_addr + c * 32, reinterpret_cast<uint32_t(&)[32]>(raw[c * 32]));
         tmem_ld_wait();
       }
-      // The scores are in registers: the MMA warp may overwrite the buffer with S_{j+2}.
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_empty);
       const int valid = p.seq_k - j * kKeys;  // keys of this block that exist
       if (valid < kKeys) {
         const float masked = negative ? INFINITY : -INFINITY;  // times the scale: -inf
@@ -322,40 +312,34 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         part[i & 7] += s[i];
       }
       total += ((part[0] + part[1]) + (part[2] + part[3])) + ((part[4] + part[5]) + (part[6] + part[7]));
-      // The group's previous P has been consumed (its P V completed) before this one overwrites it.
-      if (mine > 0 && !waited_pv) {
-        ok = mbar_wait(pv_done, (mine - 1) & 1, abort_flag, p.status, kErrAttnSoftmax);
-        ok = __all_sync(0xffffffffu, ok) != 0;
-        if (!ok) break;
-      }
+      // P as bf16 pairs over the first 64 score columns (this thread's lane): keys 2c, 2c+1 in column c.
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
+        uint32_t packed[32];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const float* e = &s[h * 64 + u * 8];
-          const uint32_t addr = p_row + h * 16384 + ((static_cast<uint32_t>(u) ^ swz) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pack2(e[0], e[1])),
-                       "r"(pack2(e[2], e[3])), "r"(pack2(e[4], e[5])), "r"(pack2(e[6], e[7]))
-                       : "memory");
-        }
+        for (int c = 0; c < 32; ++c) packed[c] = pack2(s[h * 64 + 2 * c], s[h * 64 + 2 * c + 1]);
+        tmem_st_32x32(score_addr + h * 32, packed);
       }
-      fence_proxy_async();  // generic-proxy writes of P become visible to the tensor core
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
     }
-    // The group's last P V has landed in its accumulator.
-    if (ok && mine > 0) {
-      ok = mbar_wait(pv_done, (mine - 1) & 1, abort_flag, p.status, kErrAttnSoftmax);
+    // The group's last P V has landed in its accumulator. (A group without blocks, which
+    // only happens with a single key block, waits for the other group's instead.)
+    if (ok) {
+      const uint32_t last = mine > 0 ? pv_done : smem_u32(&bars->pv_done[g ^ 1]);
+      ok = mbar_wait(last, mine > 0 ? (mine - 1) & 1 : 0, abort_flag, p.status, kErrAttnSoftmax);
       ok = __all_sync(0xffffffffu, ok) != 0;
     }
     // Merge the two groups: each row's (maximum, sum) goes through shared memory, the
     // accumulators are read from TMEM by both warps of the lane quarter, each for its
-    // half of the output columns.
-    // (The statistics reuse the group's own P tile, which its last P V has finished reading.)
-    float2* stats = reinterpret_cast<float2*>(smem_raw + (p_smem - smem_u32(smem_raw)));  // [group] at g * kPBytes
+    // half of the output columns. The statistics reuse the Q tile: whichever group gets
+    // here, the tensor core has finished every product that was issued before its last
+    // P V, and those include all that read Q.
+    float2* stats = reinterpret_cast<float2*>(smem_raw + (q_smem - smem_u32(smem_raw)));
     if (ok) {
-      stats[g * (kPBytes / sizeof(float2)) + row] = make_float2(top, total);
+      stats[g * kRows + row] = make_float2(top, total);
       tc_fence_before();
       __syncwarp();
       const uint32_t merge = smem_u32(&bars->merge[quarter]);
@@ -365,7 +349,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     }
     if (ok) {
       tc_fence_after();
-      const float2 other = stats[(g ^ 1) * (kPBytes / sizeof(float2)) + row];
+      const float2 other = stats[(g ^ 1) * kRows + row];
       const int theirs = (nb - (g ^ 1) + 1) >> 1;  // blocks the other group took
       const float common = fmaxf(top, other.x);
       const float w_mine = mine > 0 ? fast_exp2(top - common) : 0.f;
@@ -432,8 +416,8 @@ std::once_flag g_attn_attr_once[64];
 
 template <int D>
 size_t attn_smem_bytes() {
-  const size_t stages = D == 64 ? 4 : 2;
-  return 1024 + (1 + 2 * stages) * (D / 64) * 16384 + 2 * 32768 + sizeof(AttnBarriers);
+  const size_t stages = D == 64 ? 4 : 3;
+  return 1024 + (1 + 2 * stages) * (D / 64) * 16384 + sizeof(AttnBarriers);
 }
 
 }  // namespace
