@@ -302,16 +302,24 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         }
         tmem_st_wait();
       }
-      // p = 2^(scale * s - top): one FFMA and one ex2 per score, sums in eight chains.
-      const float neg_top = -top;
+      // p = 2^(scale * s - top): the multiply-add and the sums on pairs (packed f32x2:
+      // one issue slot for two scores; the softmax is bound by instruction issue), one ex2
+      // per score, sums in four chains of pairs.
+      const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2), neg_top2 = pack_f32x2(-top, -top);
+      uint64_t sums[4] = {0, 0, 0, 0};  // +0.f pairs
 #pragma unroll
-      for (int i = 0; i < 8; ++i) part[i] = 0.f;
-#pragma unroll
-      for (int i = 0; i < kKeys; ++i) {
-        s[i] = fast_exp2(fmaf(s[i], p.scale_log2, neg_top));
-        part[i & 7] += s[i];
+      for (int i = 0; i < kKeys; i += 2) {
+        float x0, x1;
+        unpack_f32x2(fma_f32x2(pack_f32x2(s[i], s[i + 1]), scale2, neg_top2), x0, x1);
+        s[i] = fast_exp2(x0);
+        s[i + 1] = fast_exp2(x1);
+        sums[(i >> 1) & 3] = add_f32x2(sums[(i >> 1) & 3], pack_f32x2(s[i], s[i + 1]));
       }
-      total += ((part[0] + part[1]) + (part[2] + part[3])) + ((part[4] + part[5]) + (part[6] + part[7]));
+      {
+        float lo, hi;
+        unpack_f32x2(add_f32x2(add_f32x2(sums[0], sums[1]), add_f32x2(sums[2], sums[3])), lo, hi);
+        total += lo + hi;
+      }
       // P as bf16 pairs over the first 64 score columns (this thread's lane): keys 2c, 2c+1 in column c.
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
