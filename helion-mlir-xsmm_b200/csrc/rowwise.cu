@@ -349,38 +349,60 @@ __global__ void __launch_bounds__(MAXT) rowwise_lean_kernel(const RowParams p) {
 #pragma unroll
         for (int j = 0; j < EPV; ++j) top = fmaxf(top, v[i][j]);
       top = row_reduce<true>(top, red_a, warps_per_row, row_in_cta, warp_in_row, lane, width);
-      float total = 0.f;
+      // (x - top) * log2e, the sums and the final scaling on pairs (packed f32x2).
+      const uint64_t neg_top2 = pack_f32x2(-top, -top), log2e2 = pack_f32x2(kLog2e, kLog2e);
+      uint64_t pair[NV][EPV / 2];
+      uint64_t total2 = 0;
 #pragma unroll
       for (int i = 0; i < NV; ++i)
 #pragma unroll
-        for (int j = 0; j < EPV; ++j) {
-          v[i][j] = fast_exp2((v[i][j] - top) * kLog2e);
-          total += v[i][j];
+        for (int j = 0; j < EPV / 2; ++j) {
+          float a, b;
+          unpack_f32x2(mul_f32x2(add_f32x2(pack_f32x2(v[i][2 * j], v[i][2 * j + 1]), neg_top2), log2e2), a, b);
+          pair[i][j] = pack_f32x2(fast_exp2(a), fast_exp2(b));
+          total2 = add_f32x2(total2, pair[i][j]);
         }
-      total = row_reduce<false>(total, red_b, warps_per_row, row_in_cta, warp_in_row, lane, width);
+      float t_lo, t_hi;
+      unpack_f32x2(total2, t_lo, t_hi);
+      const float total = row_reduce<false>(t_lo + t_hi, red_b, warps_per_row, row_in_cta, warp_in_row, lane, width);
       const float inv = 1.f / total;
+      const uint64_t inv2 = pack_f32x2(inv, inv);
 #pragma unroll
       for (int i = 0; i < NV; ++i)
 #pragma unroll
-        for (int j = 0; j < EPV; ++j) v[i][j] *= inv;
+        for (int j = 0; j < EPV / 2; ++j) unpack_f32x2(mul_f32x2(pair[i][j], inv2), v[i][2 * j], v[i][2 * j + 1]);
     } else if (OP == kGroupNorm) {
-      float s = 0.f;
+      // The arithmetic runs on pairs (packed f32x2 instructions: one issue slot for two
+      // values; the bf16 kernels are bound by instruction issue, not by HBM). Per value
+      // the operations and their order are those of the scalar form: sum, centre,
+      // sum of squares, scale, multiply-add with weight and bias.
+      uint64_t pair[NV][EPV / 2];
+      uint64_t s2 = 0;  // (+0, +0)
 #pragma unroll
       for (int i = 0; i < NV; ++i)
 #pragma unroll
-        for (int j = 0; j < EPV; ++j) s += v[i][j];
-      s = row_reduce<false>(s, red_a, warps_per_row, row_in_cta, warp_in_row, lane, width);
-      const float mean = s * inv_n;
-      float q = 0.f;
-#pragma unroll
-      for (int i = 0; i < NV; ++i)
-#pragma unroll
-        for (int j = 0; j < EPV; ++j) {
-          v[i][j] -= mean;
-          q = fmaf(v[i][j], v[i][j], q);
+        for (int j = 0; j < EPV / 2; ++j) {
+          pair[i][j] = pack_f32x2(v[i][2 * j], v[i][2 * j + 1]);
+          s2 = add_f32x2(s2, pair[i][j]);
         }
-      q = row_reduce<false>(q, red_b, warps_per_row, row_in_cta, warp_in_row, lane, width);
+      float s_lo, s_hi;
+      unpack_f32x2(s2, s_lo, s_hi);
+      const float s = row_reduce<false>(s_lo + s_hi, red_a, warps_per_row, row_in_cta, warp_in_row, lane, width);
+      const float mean = s * inv_n;
+      const uint64_t neg_mean2 = pack_f32x2(-mean, -mean);
+      uint64_t q2 = 0;
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int j = 0; j < EPV / 2; ++j) {
+          pair[i][j] = add_f32x2(pair[i][j], neg_mean2);
+          q2 = fma_f32x2(pair[i][j], pair[i][j], q2);
+        }
+      float q_lo, q_hi;
+      unpack_f32x2(q2, q_lo, q_hi);
+      const float q = row_reduce<false>(q_lo + q_hi, red_b, warps_per_row, row_in_cta, warp_in_row, lane, width);
       const float rstd = rsqrtf(q * inv_n + p.eps);
+      const uint64_t rstd2 = pack_f32x2(rstd, rstd);
       const int chan0 = p.groups > 1 ? static_cast<int>(row_c % p.groups) * static_cast<int>(p.n) : 0;
 #pragma unroll
       for (int i = 0; i < NV; ++i) {
@@ -388,22 +410,34 @@ __global__ void __launch_bounds__(MAXT) rowwise_lean_kernel(const RowParams p) {
         load_param_vec<EPV, PT>(weight + chan0 + i * col_step, w);
         load_param_vec<EPV, PT>(bias + chan0 + i * col_step, b);
 #pragma unroll
-        for (int j = 0; j < EPV; ++j) v[i][j] = fmaf(v[i][j] * rstd, w[j], b[j]);
+        for (int j = 0; j < EPV / 2; ++j)
+          unpack_f32x2(fma_f32x2(mul_f32x2(pair[i][j], rstd2), pack_f32x2(w[2 * j], w[2 * j + 1]),
+                                 pack_f32x2(b[2 * j], b[2 * j + 1])),
+                       v[i][2 * j], v[i][2 * j + 1]);
       }
     } else {
-      float q = 0.f;
+      uint64_t pair[NV][EPV / 2];
+      uint64_t q2 = 0;
 #pragma unroll
       for (int i = 0; i < NV; ++i)
 #pragma unroll
-        for (int j = 0; j < EPV; ++j) q = fmaf(v[i][j], v[i][j], q);
-      q = row_reduce<false>(q, red_a, warps_per_row, row_in_cta, warp_in_row, lane, width);
+        for (int j = 0; j < EPV / 2; ++j) {
+          pair[i][j] = pack_f32x2(v[i][2 * j], v[i][2 * j + 1]);
+          q2 = fma_f32x2(pair[i][j], pair[i][j], q2);
+        }
+      float q_lo, q_hi;
+      unpack_f32x2(q2, q_lo, q_hi);
+      const float q = row_reduce<false>(q_lo + q_hi, red_a, warps_per_row, row_in_cta, warp_in_row, lane, width);
       const float rstd = rsqrtf(q * inv_n + p.eps);
+      const uint64_t rstd2 = pack_f32x2(rstd, rstd);
 #pragma unroll
       for (int i = 0; i < NV; ++i) {
         float w[EPV];
         load_param_vec<EPV, PT>(weight + i * col_step, w);
 #pragma unroll
-        for (int j = 0; j < EPV; ++j) v[i][j] = v[i][j] * rstd * w[j];
+        for (int j = 0; j < EPV / 2; ++j)
+          unpack_f32x2(mul_f32x2(mul_f32x2(pair[i][j], rstd2), pack_f32x2(w[2 * j], w[2 * j + 1])), v[i][2 * j],
+                       v[i][2 * j + 1]);
       }
       if (warps_per_row > 1) __syncthreads();  // same two-barrier cadence as the other ops
     }
