@@ -164,6 +164,9 @@ def _make(block_sizes: tuple[int, ...] | None) -> dict[str, tuple[tuple[str, ...
         # the attention bodies of the reference's tests (tests/harness.py:263, tests/test_numerics.py:141)
         "_attention": (("q", "k", "v", "scale", "vnni"), lambda q, k, v, scale, vnni=False: ops.attention(q, k, v, float(_value(scale)))),
         "attention": (("q", "k", "v"), lambda q, k, v: ops.attention(q, k, v, 1.0)),
+        # the two-phase packed GEMM of examples/matmul_packed_mlir.py:40-60 (pack both operands
+        # into 32x32 blocks, barrier, blocked contraction): one GEMM on the operands as given
+        "_gemm_packed": (("a", "b"), lambda a, b: ops.matmul(a, b)),
     }
 
 
@@ -173,7 +176,7 @@ KNOWN_BODIES = frozenset(
     _matmul_prepacked_rows _split_k_partials _sum_partials _bmm_direct _bmm_batched _matvec_kernel _row_sum_kernel
     _row_dot_kernel _column_sum_kernel _relu_kernel _leaky_relu_kernel _scalar_mul_kernel _pad_kernel _pack_a_kernel
     _pack_a_kernel_t _pack_b_kernel _pack_b_kernel_t _pack_b_vnni_kernel _pack_b_vnni_kernel_t
-    _pack_b_vnni_panels_kernel_t _attention attention""".split()
+    _pack_b_vnni_panels_kernel_t _attention attention _gemm_packed""".split()
 )
 
 

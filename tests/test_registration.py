@@ -100,4 +100,4 @@ def test_bodies_are_matched_by_name_and_parameters() -> None:
     _row_sum_kernel_wrong.__name__ = "_row_sum_kernel"
     assert bodies.adapter_for(_row_sum_kernel_wrong, None) is None
     assert bodies.adapter_for(lambda x: x, None) is None
-    assert len(bodies.KNOWN_BODIES) == 31  # the operator set's 29 and the two attention bodies of the tests
+    assert len(bodies.KNOWN_BODIES) == 32  # the operator set's 29, the two attention bodies of the tests, the packed-GEMM example
