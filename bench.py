@@ -616,7 +616,10 @@ def main() -> None:
             "clocks": clocks,
             "kernel_status": status,
         }
-        if e2e_ms is not None:
+        if e2e_ms is not None and h2d + d2h == 0:
+            # this workload has no host-buffer leg: say so instead of repeating the device-resident number
+            line["e2e"] = None
+        elif e2e_ms is not None:
             line["e2e"] = {
                 "value": work * args.steps * world / (e2e_max * 1e-3) / scale, "unit": workload.unit,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_max / args.steps,
