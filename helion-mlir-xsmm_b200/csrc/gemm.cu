@@ -53,6 +53,7 @@ struct Resolved {
   size_t unpack_bytes;    // workspace for a packed B unpacked to [n_pad, k_pad] bf16
   size_t partial_bytes; // workspace for parallel split-K partials
   size_t split_a_bytes, split_b_bytes;  // workspace for the six-fold bf16 split of f32 operands (0: not applicable)
+  size_t split_partial_bytes;  // ... and for its K chunks as parallel partial sums (0: chunks run back to back)
 };
 
 // Whether the f32 GEMM `d` can run as a widened bf16 GEMM (layouts TMA can describe).
@@ -139,10 +140,18 @@ int validate(const b200_gemm_desc* d, Resolved* r) {
                         : 0;
   r->partial_bytes =
       d->split_k > 1 ? static_cast<size_t>(d->split_k) * d->batch * d->m * d->n * sizeof(float) : 0;
-  r->split_a_bytes = r->split_b_bytes = 0;
+  r->split_a_bytes = r->split_b_bytes = r->split_partial_bytes = 0;
   if (f32_split_applies(*d)) {
     r->split_a_bytes = static_cast<size_t>(round_up(d->m * d->k * kSplitTerms * 2, 256));
     r->split_b_bytes = static_cast<size_t>(round_up(d->n * d->k * kSplitTerms * 2, 256));
+    // Few output tiles: the K chunks of the widened product (added in f32 either way, in
+    // the same order) run as parallel work items into partial sums, so that the chunks of
+    // one tile occupy several SMs instead of running back to back on one.
+    const int64_t chunks = ceil_div(d->k * kSplitTerms, kSplitChunkK);
+    const int64_t pair_tiles = ceil_div(d->m, 256) * ceil_div(d->n, 256);
+    const int64_t pairs = device_info().sm_count / 2;
+    if (chunks > 1 && pair_tiles * chunks <= pairs)
+      r->split_partial_bytes = static_cast<size_t>(round_up(chunks * d->m * d->n * 4, 256));
   }
   return 0;
 }
@@ -225,7 +234,7 @@ using namespace b200;
 extern "C" size_t b200_gemm_workspace_bytes(const b200_gemm_desc* desc) {
   Resolved r{};
   if (validate(desc, &r) != 0 || desc->m == 0 || desc->n == 0) return 0;
-  return r.unpack_a_bytes + r.unpack_bytes + r.partial_bytes + r.split_a_bytes + r.split_b_bytes;
+  return r.unpack_a_bytes + r.unpack_bytes + r.partial_bytes + r.split_a_bytes + r.split_b_bytes + r.split_partial_bytes;
 }
 
 extern "C" int b200_gemm(const b200_gemm_desc* desc, void* stream) {
@@ -265,7 +274,10 @@ extern "C" int b200_gemm(const b200_gemm_desc* desc, void* stream) {
       rc = launch_split_f32(static_cast<const float*>(d.b), wide + r.split_a_bytes, b_cols ? d.n : d.k,
                             b_cols ? d.k : d.n, d.ldb, true, b_cols, s);
     if (rc != 0) return finish(rc);
-    return run_gemm_umma(split_desc(d, wide, wide + r.split_a_bytes), r.epi, nullptr, s);
+    float* chunk_partials = nullptr;
+    if (r.split_partial_bytes && d.workspace_bytes >= r.split_a_bytes + r.split_b_bytes + r.split_partial_bytes)
+      chunk_partials = reinterpret_cast<float*>(wide + r.split_a_bytes + r.split_b_bytes);
+    return run_gemm_umma(split_desc(d, wide, wide + r.split_a_bytes), r.epi, chunk_partials, s);
   }
 
   if (path == kPathUmmaUnpack) {

@@ -563,7 +563,12 @@ UmmaPlan umma_plan(const b200_gemm_desc& d, int sm_count, bool parallel_splits) 
   // 32 at a time; an N-contiguous B arrives in 64-column TMA chunks).
   const int gran = 64;
   int bn = 256;
-  if (d.tile_n > 0) bn = static_cast<int>(round_up(d.tile_n, 64));
+  // tile_n > 0 is a hint (a Helion config's block_sizes): taken when it asks for at least 128
+  // columns, the narrowest tile that keeps the tensor core reasonably busy; smaller hints
+  // (written for a CPU's register tiles) leave the choice to the launcher. tile_n < 0 fixes
+  // the width to -tile_n (tuning runs).
+  const bool fixed_n = d.tile_n < 0 || d.tile_n >= 128;
+  if (fixed_n) bn = static_cast<int>(round_up(d.tile_n < 0 ? -static_cast<int64_t>(d.tile_n) : d.tile_n, 64));
   if (bn > 256) bn = 256;
   // Narrow problems: no wider than N needs.
   const int64_t n_cap = round_up(d.n, gran);
@@ -573,7 +578,7 @@ UmmaPlan umma_plan(const b200_gemm_desc& d, int sm_count, bool parallel_splits) 
   // measured 0.65 of its throughput, so idle SMs cost less than narrow tiles
   // (2048x2048x8192: 1320 TFLOP/s at 256 columns on 128 of 148 SMs, 744 at 128 columns).
   const int64_t psplit_factor = (parallel_splits && d.split_k > 1) ? d.split_k : 1;
-  while (d.tile_n <= 0 && bn > 64 &&
+  while (!fixed_n && bn > 64 &&
          ceil_div(d.m, kBlockM) * ceil_div(d.n, bn) * d.batch * psplit_factor * 8 < sm_count)
     bn = static_cast<int>(round_up(bn / 2, gran));
   plan.block_n = bn;

@@ -479,7 +479,7 @@ def _matmul_plan(
         force_kernel = 0
         if picked is not None:
             if picked.tile_n:
-                tiles = (_TILE_M, picked.tile_n, _TILE_K)
+                tiles = (_TILE_M, -picked.tile_n, _TILE_K)  # negative: exactly this width, not a hint
             force_kernel = picked.force_kernel()
             if picked.split_k > 1 and plain and splits is None:
                 splits = picked.split_k

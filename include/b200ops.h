@@ -111,7 +111,10 @@ typedef struct b200_gemm_desc {
    * >1 with a workspace of S*batch*M*N floats: partial products are written
    * there by parallel CTAs and summed in the order s=0..S-1 by a second kernel. */
   int32_t split_k;
-  int32_t tile_m, tile_n, tile_k;        /* block_sizes hint (0: choose); snapped to what the kernels implement */
+  int32_t tile_m, tile_n, tile_k;        /* block_sizes hint (0: choose). tile_n >= 128 is snapped to a multiple of
+                                          * 64 <= 256 and used; smaller positive hints leave the choice to the
+                                          * launcher; tile_n < 0 fixes the width to -tile_n (tuning). tile_m and
+                                          * tile_k are accepted and ignored: rows are 128 per CTA, K stages 64. */
   void* workspace;
   size_t workspace_bytes;
   int32_t force_kernel;  /* 0 auto, 1 tensor-core (tcgen05) path or refuse, 2 SIMT FFMA path,
