@@ -177,3 +177,31 @@ def test_elementwise(ops, shape, dtype) -> None:
     assert torch.equal(bits(ops.scalar_mul(dx, torch.tensor(-0.25))), bits(x * -0.25))
     odd = cuda(torch.randn(1025, generator=gen).to(dtype))[1:]  # unaligned base
     assert torch.equal(bits(ops.relu(odd)), bits(torch.relu(odd.cpu())))
+
+
+def test_seeded_shape_sweep(ops) -> None:
+    """Random row counts and lengths (log-uniform up to 70000 columns) through softmax,
+    layer_norm and rms_norm in both dtypes: every threads-per-row choice from 4 to 1024,
+    masked and whole vectors, and the long-row kernel."""
+    import math
+    import random
+
+    rng = random.Random(2024)
+    gen = torch.Generator().manual_seed(2024)
+    for case in range(36):
+        n = max(1, int(math.exp(rng.uniform(0.0, math.log(70000.0)))))
+        if case % 3 == 0:
+            n = max(8, n // 8 * 8)  # whole 16-byte vectors in both dtypes
+        m = rng.randint(1, max(1, min(300, 400000 // n)))
+        x = torch.randn(m, n, generator=gen) * rng.choice([0.5, 3.0, 20.0])
+        w, b = torch.randn(n, generator=gen), torch.randn(n, generator=gen)
+        for dtype in (F32, BF16):
+            xd, wd, bd = x.to(dtype), w.to(dtype), b.to(dtype)
+            dx = cuda(xd)
+            what = f"{m}x{n} {dtype}"
+            sm = ops.softmax(dx).cpu()
+            assert checks.max_norm_rel(sm, ref.softmax(xd)) < tol(dtype), "softmax " + what
+            ln = ops.layer_norm(dx, cuda(wd), cuda(bd), 1e-5).cpu()
+            checks.assert_parity(dtype, ln, ref.layer_norm(xd, wd, bd, 1e-5).float(), "layer_norm " + what)
+            rn = ops.rms_norm(dx, cuda(wd), 1e-5).cpu()
+            checks.assert_parity(dtype, rn, ref.rms_norm(xd, wd, 1e-5).float(), "rms_norm " + what)
