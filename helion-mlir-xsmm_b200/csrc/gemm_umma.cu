@@ -305,6 +305,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (lane == 0 && leader) {
       uint32_t stage = 0, parity = 0;
       uint32_t phase = 0;
+      bool landed = false;
       const uint32_t stage_step = stage_bytes >> 4;
       bool ok = true;
       for (int64_t work = first_work; work < total_work && ok; work += work_stride) {
@@ -318,24 +319,27 @@ __global__ void __launch_bounds__(kThreads, 1)
           const uint32_t d_tmem = tmem_base + acc * kAccStride;
           uint32_t accumulate = 0;
           for (int kb = 0; kb < p.k_blocks; ++kb) {
-            ok = mbar_wait(smem_u32(&bars->full[stage]), parity, abort_flag, p.status, kErrMmaWait);
-            if (!ok) break;
+            // `landed`: the previous block's MMAs carried a test of this stage's barrier along
+            // (umma_bf16_x4_peek), so the usual case costs no barrier round trip here.
+            if (!landed) {
+              ok = mbar_wait(smem_u32(&bars->full[stage]), parity, abort_flag, p.status, kErrMmaWait);
+              if (!ok) break;
+            }
             tc_fence_after();
             const uint64_t a_desc =
                 make_desc(smem_base, p.a_desc_lbo, p.a_desc_hi) + static_cast<uint64_t>(stage * stage_step);
             const uint64_t b_desc = make_desc(smem_base + p.a_stage_bytes, p.b_desc_lbo, p.b_desc_hi) +
                                     static_cast<uint64_t>(stage * stage_step);
-#pragma unroll
-            for (int j = 0; j < kStageK / kUmmaK; ++j) {
-              umma_bf16<CG>(d_tmem, a_desc + static_cast<uint64_t>(j * p.a_kstep),
-                            b_desc + static_cast<uint64_t>(j * p.b_kstep), p.idesc, accumulate);
-              accumulate = 1;
-            }
-            umma_commit<CG>(smem_u32(&bars->empty[stage]));
+            const uint32_t this_stage = stage;
             if (++stage == static_cast<uint32_t>(p.stages)) {
               stage = 0;
               parity ^= 1u;
             }
+            // (after the last block of the last tile the tested barrier is simply never armed again)
+            landed = umma_bf16_x4_peek<CG>(d_tmem, a_desc, b_desc, p.a_kstep, p.b_kstep, p.idesc, accumulate,
+                                           smem_u32(&bars->full[stage]), parity) != 0;
+            accumulate = 1;
+            umma_commit<CG>(smem_u32(&bars->empty[this_stage]));
           }
           if (ok) umma_commit<CG>(smem_u32(&bars->acc_full[acc]));
         }

@@ -149,6 +149,56 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// The four MMAs of a 64-deep K block, preceded by a non-blocking test of another
+// barrier whose result is only looked at after the MMAs: the test's latency then
+// overlaps the issue of the MMAs instead of sitting between two K blocks (the tensor
+// core idles for every cycle the issuing thread spends between blocks). Returns
+// whether the tested phase had completed. `first_accumulate`: 0 overwrites the
+// accumulator with the first product.
+template <int CG>
+__device__ __forceinline__ uint32_t umma_bf16_x4_peek(uint32_t d_tmem, uint64_t a0, uint64_t b0, uint64_t a_step,
+                                                      uint64_t b_step, uint32_t idesc, uint32_t first_accumulate,
+                                                      uint32_t peek_bar, uint32_t peek_parity) {
+  uint32_t ready;
+  const uint64_t a1 = a0 + a_step, a2 = a1 + a_step, a3 = a2 + a_step;
+  const uint64_t b1 = b0 + b_step, b2 = b1 + b_step, b3 = b2 + b_step;
+  if (CG == 1)
+    asm volatile(
+        "{\n\t"
+        ".reg .pred ready, first, always;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 ready, [%1], %2;\n\t"
+        "setp.ne.b32 first, %3, 0;\n\t"
+        "setp.eq.b32 always, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%4], %5, %6, %7, first;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%4], %8, %9, %7, always;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%4], %10, %11, %7, always;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%4], %12, %13, %7, always;\n\t"
+        "selp.u32 %0, 1, 0, ready;\n\t"
+        "}"
+        : "=r"(ready)
+        : "r"(peek_bar), "r"(peek_parity), "r"(first_accumulate), "r"(d_tmem), "l"(a0), "l"(b0), "r"(idesc), "l"(a1),
+          "l"(b1), "l"(a2), "l"(b2), "l"(a3), "l"(b3)
+        : "memory");
+  else
+    asm volatile(
+        "{\n\t"
+        ".reg .pred ready, first, always;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 ready, [%1], %2;\n\t"
+        "setp.ne.b32 first, %3, 0;\n\t"
+        "setp.eq.b32 always, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%4], %5, %6, %7, first;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%4], %8, %9, %7, always;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%4], %10, %11, %7, always;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%4], %12, %13, %7, always;\n\t"
+        "selp.u32 %0, 1, 0, ready;\n\t"
+        "}"
+        : "=r"(ready)
+        : "r"(peek_bar), "r"(peek_parity), "r"(first_accumulate), "r"(d_tmem), "l"(a0), "l"(b0), "r"(idesc), "l"(a1),
+          "l"(b1), "l"(a2), "l"(b2), "l"(a3), "l"(b3)
+        : "memory");
+  return ready;
+}
+
 // The same product with the A operand in tensor memory (lane = row, each 32-bit
 // column two consecutive K elements; K = 16 per instruction = 8 columns) and B in
 // shared memory. cta_group::1 only.
