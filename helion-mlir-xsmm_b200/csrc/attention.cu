@@ -176,52 +176,73 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       bool ok = mbar_wait(smem_u32(&bars->q_full), 0, abort_flag, p.status, kErrAttnMma);
       tc_fence_after();
       const uint64_t q_desc = make_desc(q_smem, 1u, hi);
+      // Barriers that are normally complete long before they are needed (the K and V
+      // stages) are tested alongside the MMAs issued before them, so that no barrier
+      // round trip sits between two groups of MMAs; `k_landed` / `v_landed` carry the result.
+      bool k_landed = false, v_landed = false;
       // S_j = Q K_j^T into score buffer j % 2: both operands K-major, D/16 MMAs of K = 16.
-      auto issue_scores = [&](int j) -> bool {
+      // `peek_v`: the block whose V stage is tested on the way (its P V comes next).
+      auto issue_scores = [&](int j, int peek_v) -> bool {
         const uint32_t st = j % kStages, g = j & 1;
-        if (!mbar_wait(smem_u32(&bars->k_full[st]), (j / kStages) & 1, abort_flag, p.status, kErrAttnMma)) return false;
+        if (!k_landed &&
+            !mbar_wait(smem_u32(&bars->k_full[st]), (j / kStages) & 1, abort_flag, p.status, kErrAttnMma))
+          return false;
+        k_landed = false;
         tc_fence_after();
         const uint64_t k_desc = make_desc(k_smem + st * kTileBytes, 1u, hi);
-        uint32_t accumulate = 0;
+        const uint32_t d_tmem = tmem_base + g * kScoreCols;
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) {
+          const uint64_t step = static_cast<uint64_t>((c * 16384) >> 4);
+          if (c + 1 < kChunks || peek_v < 0) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const uint64_t step = static_cast<uint64_t>((c * 16384 + i * 32) >> 4);
-            umma_bf16<1>(tmem_base + g * kScoreCols, q_desc + step, k_desc + step, p.idesc_qk, accumulate);
-            accumulate = 1;
+            for (int i = 0; i < 4; ++i)
+              umma_bf16<1>(d_tmem, q_desc + step + static_cast<uint64_t>((i * 32) >> 4),
+                           k_desc + step + static_cast<uint64_t>((i * 32) >> 4), p.idesc_qk, (c | i) ? 1u : 0u);
+          } else {
+            v_landed = umma_bf16_x4_peek<1>(d_tmem, q_desc + step, k_desc + step, 32 >> 4, 32 >> 4, p.idesc_qk,
+                                            c ? 1u : 0u, smem_u32(&bars->v_full[peek_v % kStages]),
+                                            (peek_v / kStages) & 1) != 0;
           }
         }
         umma_commit<1>(smem_u32(&bars->k_empty[st]));
         umma_commit<1>(smem_u32(&bars->s_full[g]));
         return true;
       };
-      if (ok && nb > 0) ok = issue_scores(0);
-      if (ok && nb > 1) ok = issue_scores(1);
+      if (ok && nb > 0) ok = issue_scores(0, nb > 1 ? -1 : 0);
+      if (ok && nb > 1) ok = issue_scores(1, 0);
       for (int j = 0; j < nb && ok; ++j) {
         // O_g += P_j V_j: P from tensor memory (8 columns = 16 keys per MMA), V MN-major
         // in shared memory (64-key halves of D/64 chunks).
         const uint32_t st = j % kStages, g = j & 1;
-        ok = mbar_wait(smem_u32(&bars->v_full[st]), (j / kStages) & 1, abort_flag, p.status, kErrAttnMma);
+        if (!v_landed) ok = mbar_wait(smem_u32(&bars->v_full[st]), (j / kStages) & 1, abort_flag, p.status, kErrAttnMma);
+        v_landed = false;
         if (ok) ok = mbar_wait(smem_u32(&bars->p_full[g]), (j >> 1) & 1, abort_flag, p.status, kErrAttnMma);
         if (!ok) break;
         tc_fence_after();
-        uint32_t accumulate = j > 1 ? 1u : 0u;
+        const uint32_t d_tmem = tmem_base + kOutCol + g * D, p_tmem = tmem_base + g * kScoreCols;
+        const uint64_t v_lo = make_desc(v_smem + st * kTileBytes, 8192u >> 4, hi);
+        const uint64_t v_hi = make_desc(v_smem + st * kTileBytes + kVHalfBytes, 8192u >> 4, hi);
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const uint64_t v_desc = make_desc(v_smem + st * kTileBytes + h * kVHalfBytes, 8192u >> 4, hi);
+        for (int i = 0; i < 4; ++i)
+          umma_bf16_ts(d_tmem, p_tmem + i * 8, v_lo + static_cast<uint64_t>((i * 2048) >> 4), p.idesc_pv,
+                       (j > 1 || i > 0) ? 1u : 0u);
+        if (j + 2 < nb) {
+          // the second half carries the test of the K stage the next scores need
+          const int jn = j + 2;
+          k_landed = umma_bf16_ts_x4_peek(d_tmem, p_tmem + 32, v_hi, 2048 >> 4, p.idesc_pv, 1u,
+                                          smem_u32(&bars->k_full[jn % kStages]), (jn / kStages) & 1) != 0;
+        } else {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            umma_bf16_ts(tmem_base + kOutCol + g * D, tmem_base + g * kScoreCols + (h * 4 + i) * 8,
-                         v_desc + static_cast<uint64_t>((i * 2048) >> 4), p.idesc_pv, accumulate);
-            accumulate = 1;
-          }
+          for (int i = 0; i < 4; ++i)
+            umma_bf16_ts(d_tmem, p_tmem + 32 + i * 8, v_hi + static_cast<uint64_t>((i * 2048) >> 4), p.idesc_pv, 1u);
         }
         umma_commit<1>(smem_u32(&bars->v_empty[st]));
         umma_commit<1>(smem_u32(&bars->pv_done[g]));
         // The next scores of this group go where P_j lies: issued after the P V that reads
-        // it, and the tensor core runs what one thread issues in order.
-        if (j + 2 < nb) ok = issue_scores(j + 2);
+        // it, and the tensor core runs what one thread issues in order. On the way they
+        // test the V stage of block j + 1, whose P V is next.
+        if (j + 2 < nb) ok = issue_scores(j + 2, j + 1);
       }
     }
     __syncwarp();

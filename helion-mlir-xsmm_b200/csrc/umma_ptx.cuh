@@ -213,6 +213,32 @@ __device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, u
       "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Four such MMAs over consecutive K slices (A advancing by 8 tensor-memory columns, B by
+// `b_step` descriptor units), with the same carried barrier test as umma_bf16_x4_peek.
+__device__ __forceinline__ uint32_t umma_bf16_ts_x4_peek(uint32_t d_tmem, uint32_t a_tmem, uint64_t b0, uint64_t b_step,
+                                                         uint32_t idesc, uint32_t first_accumulate, uint32_t peek_bar,
+                                                         uint32_t peek_parity) {
+  uint32_t ready;
+  const uint64_t b1 = b0 + b_step, b2 = b1 + b_step, b3 = b2 + b_step;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred ready, first, always;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 ready, [%1], %2;\n\t"
+      "setp.ne.b32 first, %3, 0;\n\t"
+      "setp.eq.b32 always, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%4], [%5], %9, %8, first;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%4], [%6], %10, %8, always;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%4], [%7], %11, %8, always;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%4], [%13], %12, %8, always;\n\t"
+      "selp.u32 %0, 1, 0, ready;\n\t"
+      "}"
+      : "=r"(ready)
+      : "r"(peek_bar), "r"(peek_parity), "r"(first_accumulate), "r"(d_tmem), "r"(a_tmem), "r"(a_tmem + 8),
+        "r"(a_tmem + 16), "r"(idesc), "l"(b0), "l"(b1), "l"(b2), "l"(b3), "r"(a_tmem + 24)
+      : "memory");
+  return ready;
+}
+
 // Arrives on `bar` once every tcgen05.mma issued so far by this thread has
 // completed; for a CTA pair, on the barrier at that offset in both CTAs.
 template <int CG>
