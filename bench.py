@@ -516,7 +516,7 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=20)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
-    parser.add_argument("--rows", type=int, default=0, help="rows per GPU of the c2/c4 workloads, heads per GPU of attn (default: the configuration's; smaller sizes are for profiler captures, not for reported numbers)")
+    parser.add_argument("--rows", type=int, default=0, help="rows per GPU of the c2/c4 workloads, heads per GPU of attn, batches per GPU of c5 (default: the configuration's; smaller sizes are for profiler captures, not for reported numbers)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-e2e", action="store_true")
     args = parser.parse_args()
@@ -524,10 +524,12 @@ def main() -> None:
 
     rank, world, local_rank = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
     workload: Workload = WORKLOADS[args.workload]()
-    if args.rows > 0 and hasattr(workload, "M"):
-        workload.M = args.rows
-    if args.rows > 0 and hasattr(workload, "H"):
-        workload.H = args.rows
+    if args.rows > 0:
+        # the one size of the workload that shards: batches, else heads, else rows
+        for name in ("B", "H", "M"):
+            if hasattr(workload, name):
+                setattr(workload, name, args.rows)
+                break
     if args.impl == "reference":
         run_reference(args, workload, rank)
         return
@@ -639,9 +641,9 @@ def main() -> None:
 TRAFFIC: dict[str, float | None] = {
     "c1": None,
     "c2": 158.1e6,  # gemm_umma_bf16_kernel<2>: 111.7 MB read + 46.5 MB written (algorithmic 167.8 MB)
-    "c3": None,
+    "c3": 1509.7e6,  # gemm_umma_bf16_kernel<2> of the step: 1256 MB read + 253.7 MB written (operands streamed 4.7 times)
     "c4": 860.1e6,  # f32 softmax, scaled x4 from the 8192-row capture (134.26 MB read + 80.77 MB written)
-    "c5": None,
+    "c5": 2216.6e6,  # 37-batch capture (1258.5 MB read + 23.0 MB written) scaled to 64 batches
     "attn": None,
 }
 
