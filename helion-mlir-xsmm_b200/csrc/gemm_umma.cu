@@ -618,6 +618,25 @@ UmmaPlan umma_plan(const b200_gemm_desc& d, int sm_count, bool parallel_splits) 
 
 // `partials`: NULL, or room for split_k * batch * m * n floats: the K splits then
 // run as parallel work items and the ordered reduction applies the epilogue.
+// Batches to peel off the end of a batched problem and run as a second launch with
+// 128-column tiles, or 0. A persistent grid of CTA pairs runs ceil(tiles / pairs) rounds
+// of tiles; when the last round would be less than half full and the batches it holds
+// fit one round of half-width tiles, that round costs ~0.7 of a full one instead of 1
+// (C5: 256 tiles on 74 pairs are 3.46 rounds, run as 4; peeled: 3 + one round of 72
+// half-width tiles).
+int64_t tail_batches(const b200_gemm_desc& d, const UmmaPlan& plan, int sm_count) {
+  if (d.batch < 2 || plan.cta_group != 2 || plan.block_n != 256 || plan.psplits != 1 || d.tile_n != 0) return 0;
+  if (d.n % 256 != 0) return 0;  // the half-width tiles must split every column tile in two
+  const int64_t pairs = sm_count / 2;
+  const int64_t per_batch = ceil_div(d.m, 2 * kBlockM) * ceil_div(d.n, plan.block_n);
+  const int64_t work = per_batch * d.batch;
+  const int64_t full_rounds = work / pairs, excess = work - full_rounds * pairs;
+  if (full_rounds < 1 || excess == 0 || excess * 2 > pairs) return 0;
+  const int64_t peel = ceil_div(excess, per_batch);
+  if (peel >= d.batch || peel * per_batch * 2 > pairs) return 0;
+  return peel;
+}
+
 int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* partials, cudaStream_t stream) {
   const DeviceInfo& dev = device_info();
   if (dev.sm_count == 0) return refuse(B200_E_DEVICE);
@@ -625,6 +644,22 @@ int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* parti
   const bool b_kmajor = d.b_layout == B200_LAYOUT_COL;  // [N,K]: K contiguous
   const bool parallel = partials != nullptr && d.split_k > 1;
   const UmmaPlan plan = umma_plan(d, dev.sm_count, parallel);
+  if (const int64_t peel = parallel ? 0 : tail_batches(d, plan, dev.sm_count)) {
+    b200_gemm_desc head = d, tail = d;
+    head.batch = d.batch - peel;
+    head.tile_n = -256;  // fixed widths: neither part is planned (or peeled) again
+    tail.batch = peel;
+    tail.tile_n = -128;
+    const int64_t out_size = d.out_dtype == B200_BF16 ? 2 : 4;
+    tail.a = static_cast<const uint8_t*>(d.a) + head.batch * d.stride_a * 2;
+    tail.b = static_cast<const uint8_t*>(d.b) + head.batch * d.stride_b * 2;
+    tail.c = static_cast<uint8_t*>(d.c) + head.batch * d.stride_c * out_size;
+    int rc = run_gemm_umma(head, epi, nullptr, stream);
+    if (rc != 0) return rc;
+    rc = run_gemm_umma(tail, epi, nullptr, stream);
+    if (rc == 0) counters().calls.fetch_sub(1, std::memory_order_relaxed);  // one call, two launches
+    return rc;
+  }
 
   CUtensorMap map_a, map_b;
   bool ok;
@@ -730,9 +765,12 @@ int explain_gemm_umma(const b200_gemm_desc& d, char* buf, size_t len) {
   const DeviceInfo& dev = device_info();
   const bool parallel = d.workspace != nullptr && d.split_k > 1;
   const UmmaPlan plan = umma_plan(d, dev.sm_count > 0 ? dev.sm_count : 148, parallel);
-  snprintf(buf, len, "umma_bf16 cta_group=%d tile=%dx%dx%d stages=%d serial_splits=%d parallel_splits=%d grid=%u smem=%zu",
-           plan.cta_group, kBlockM * plan.cta_group, plan.block_n, kStageK, plan.stages, plan.splits, plan.psplits,
-           plan.grid, plan.smem);
+  const int64_t peel = parallel ? 0 : tail_batches(d, plan, dev.sm_count > 0 ? dev.sm_count : 148);
+  int used = snprintf(buf, len, "umma_bf16 cta_group=%d tile=%dx%dx%d stages=%d serial_splits=%d parallel_splits=%d grid=%u smem=%zu",
+                      plan.cta_group, kBlockM * plan.cta_group, plan.block_n, kStageK, plan.stages, plan.splits, plan.psplits,
+                      plan.grid, plan.smem);
+  if (peel > 0 && used > 0 && static_cast<size_t>(used) < len)
+    snprintf(buf + used, len - used, " tail_batches=%lld as a second launch with 128-column tiles", static_cast<long long>(peel));
   return 0;
 }
 

@@ -645,7 +645,7 @@ int dispatch_vpt(const RowParams& p, int vpt, int cta_threads, cudaStream_t stre
     case 16:
       return launch_rowwise<T, VEC, 16, OP, 256>(p, cta_threads, stream);
     default:
-      if (cta_threads > 256) return launch_rowwise<T, VEC, 32, OP, 1024>(p, cta_threads, stream);
+      if (cta_threads > 256) return launch_rowwise<T, VEC, 32, OP, 512>(p, cta_threads, stream);  // tpr = 512: 128 registers per thread, no spills
       return launch_rowwise<T, VEC, 32, OP, 256>(p, cta_threads, stream);
   }
 }

@@ -103,6 +103,26 @@ def test_output_type_and_f32_vectors(ops) -> None:
     assert checks.rel_frobenius(out.cpu(), ref.matmul(x, w, trans_b=True, bias=bias, out_dtype=F32)) < 1e-5
 
 
+def test_bmm_tail_batches_run_with_half_width_tiles(ops) -> None:
+    """More 256x256 tiles than CTA pairs, with a last round less than half full: the batches of
+    that round go to a second launch with 128-column tiles. Same results as the oracle, and the
+    same bits as each batch computed on its own (no K split: the tile width does not change a sum)."""
+    pairs = torch.cuda.get_device_properties(0).multi_processor_count // 2
+    batch = pairs + 6
+    gen = torch.Generator().manual_seed(29)
+    a, b = rand(gen, batch, 256, 192), rand(gen, batch, 192, 256)
+    da, db = cuda(a, b)
+    text = str(ops.bmm.explain(da, db)) if hasattr(ops.bmm, "explain") else ""
+    out = ops.bmm(da, db)
+    checks.assert_parity(BF16, out.cpu(), ref.bmm(a, b), "bmm with peeled tail")
+    assert torch.equal(out[-1], ops.matmul(da[-1], db[-1]))
+    assert torch.equal(out[0], ops.matmul(da[0], db[0]))
+    if text:
+        assert "tail_batches=6" in text
+    split = ops.bmm(da, db, split_k=3, out_dtype=F32)
+    assert checks.rel_frobenius(split.cpu(), ref.bmm(a, b, split_k=3, out_dtype=F32)) < 1e-5
+
+
 def test_bmm_and_split_k(ops) -> None:
     gen = torch.Generator().manual_seed(13)
     a, b = rand(gen, 6, 256, 512), rand(gen, 6, 512, 128)
