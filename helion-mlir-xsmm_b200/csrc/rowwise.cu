@@ -664,7 +664,10 @@ int run_rowwise(RowParams p, cudaStream_t stream) {
   const int per_unit = vec ? kvec : 1;
   // Threads per row: up to 256 at 16 values per thread, then 32 values per
   // thread, then wider CTAs (which are held to 64 registers per thread).
-  const int units16 = 16 / per_unit > 0 ? 16 / per_unit : 1, units32 = 32 / per_unit;
+  // (bf16 rows aim at 32 values per thread from the start: 64 bytes of loads in flight per
+  // thread, as for f32, and half as many warps to reduce across)
+  const int first = sizeof(T) == 2 && vec ? 32 : 16;
+  const int units16 = first / per_unit > 0 ? first / per_unit : 1, units32 = 32 / per_unit;
   // Rows of less than a warp's worth of values share a warp (down to 4 threads per row).
   int tpr = 4;
   while (tpr < 256 && static_cast<int64_t>(tpr) * units16 < units) tpr <<= 1;
