@@ -139,7 +139,7 @@ int run_row_reduce(int kind, ReduceParams p, cudaStream_t stream) {
 // ---------------------------------------------------------------------------
 
 constexpr int kColThreads = 128;
-constexpr int kColTargetCtas = 592;  // four CTAs per SM of a 148-SM part, for strips of 512 columns
+constexpr int kColTargetCtas = 1024;  // about seven CTAs per SM of a 148-SM part, for strips of 512 columns; 1024 x 512 partial sums = 2 MiB
 constexpr int kColMinRows = 64;
 
 struct ColPlan {
@@ -155,8 +155,11 @@ ColPlan column_plan(int64_t m, int64_t n, int cpt) {
   ColPlan plan;
   plan.cols_per_thread = cpt;
   const int64_t units = ceil_div(n, static_cast<int64_t>(plan.cols_per_thread));
+  // Strips are 512 columns at most (64 threads of 8 bf16 columns, the CTA's other 64 taking
+  // every other row): a strip of 1024 left two CTAs per SM, too few bytes in flight for HBM.
+  const int side = cpt == 8 ? kColThreads / 2 : kColThreads;
   plan.tpr_log2 = 0;
-  while ((1 << plan.tpr_log2) < kColThreads && (int64_t(1) << plan.tpr_log2) < units) ++plan.tpr_log2;
+  while ((1 << plan.tpr_log2) < side && (int64_t(1) << plan.tpr_log2) < units) ++plan.tpr_log2;
   plan.col_tiles = ceil_div(units, int64_t(1) << plan.tpr_log2);
   // Wider strips get fewer row chunks, so the partial sums (chunks x n floats) stay
   // within kColTargetCtas x 512 floats whatever the strip width.
@@ -234,12 +237,26 @@ __global__ void __launch_bounds__(kColThreads) column_partial_kernel(const T* __
   for (int j = 0; j < CPT; ++j) d[j] = acc[j];
 }
 
-__global__ void column_final_kernel(const float* __restrict__ partial, float* __restrict__ out, int64_t n,
-                                    int64_t chunks) {
-  const int64_t col = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (col >= n) return;
-  float acc = partial[col];
-  for (int64_t s = 1; s < chunks; ++s) acc += partial[s * n + col];
+// Stage 2: 32 columns x 8 thread rows per CTA. Thread row r adds the partial sums of the
+// chunks r, r + 8, ... in ascending order, then the eight rows are added in order: a fixed
+// order, and a column's chain of dependent loads is an eighth as long as with one thread
+// per column (1048576 x 64: the single CTA of 64 threads took most of the call).
+constexpr int kFinalCols = 32, kFinalRows = 8;
+__global__ void __launch_bounds__(kFinalCols * kFinalRows)
+    column_final_kernel(const float* __restrict__ partial, float* __restrict__ out, int64_t n, int64_t chunks) {
+  __shared__ float red[kFinalRows][kFinalCols];
+  const int tc = threadIdx.x & (kFinalCols - 1), tr = threadIdx.x / kFinalCols;
+  const int64_t col = static_cast<int64_t>(blockIdx.x) * kFinalCols + tc;
+  float acc = 0.f;
+  if (col < n) {
+#pragma unroll 4
+    for (int64_t s = tr; s < chunks; s += kFinalRows) acc += partial[s * n + col];
+  }
+  red[tr][tc] = acc;
+  __syncthreads();
+  if (tr != 0 || col >= n) return;
+#pragma unroll
+  for (int r = 1; r < kFinalRows; ++r) acc += red[r][tc];
   out[col] = acc;
 }
 
@@ -285,8 +302,8 @@ int column_sum_impl(int32_t dtype, const void* x, float* out, int64_t m, int64_t
       launch(column_partial_kernel<__nv_bfloat16, 1, true>, column_partial_kernel<__nv_bfloat16, 1, false>, xs);
   }
   if (plan.chunks > 1) {
-    const unsigned blocks = static_cast<unsigned>(ceil_div(n, 256));
-    column_final_kernel<<<blocks, 256, 0, stream>>>(stage1, out, n, plan.chunks);
+    const unsigned blocks = static_cast<unsigned>(ceil_div(n, kFinalCols));
+    column_final_kernel<<<blocks, kFinalCols * kFinalRows, 0, stream>>>(stage1, out, n, plan.chunks);
     return launched(2);
   }
   return launched(1);

@@ -239,8 +239,8 @@ int b200_column_sum(int32_t dtype, const void* x, float* out, int64_t m, int64_t
  *
  * - Shapes whose partial sums (b200_column_sum_workspace_bytes(m, n)) exceed the
  *   array are refused with B200_E_TOO_LARGE; nothing runs. With the present
- *   two-stage plan (row chunks x columns of at most 592 x 512 partial sums) no shape needs
- *   more than 1,212,416 bytes, so the 2 MiB array holds every shape; the check is
+ *   two-stage plan (row chunks x columns of at most 1024 x 512 partial sums) no shape needs
+ *   more than 2,097,152 bytes, which the 2 MiB array just holds; the check is
  *   what keeps that true if the plan's constants change.
  * - The first call on each device looks up the array's device address
  *   (cudaGetSymbolAddress, with that device current). Make that first call outside
