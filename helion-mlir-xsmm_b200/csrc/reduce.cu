@@ -100,19 +100,41 @@ __global__ void __launch_bounds__(256) row_reduce_kernel(const ReduceParams p) {
   }
 }
 
+// CTAs of 256 threads that fit one SM, asked of the runtime once per instantiation: the
+// grid is persistent (rows strided by the grid), so CTAs beyond what is resident would run
+// as a second, mostly empty round (row_dot on bf16 rows needs 40 registers: six CTAs per
+// SM, and with a grid of eight per SM it ran at half the bandwidth of row_sum).
+template <typename T, bool VEC, int KIND>
+int resident_ctas_per_sm() {
+  static const int per_sm = [] {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, row_reduce_kernel<T, VEC, KIND>, 256, 0) != cudaSuccess || n < 1) {
+      cudaGetLastError();
+      n = 4;
+    }
+    return n;
+  }();
+  return per_sm;
+}
+
+template <typename T, bool VEC, int KIND>
+int launch_row_reduce_kind(const ReduceParams& p, int64_t wanted, int sm_count, cudaStream_t stream) {
+  const int64_t resident = static_cast<int64_t>(sm_count) * resident_ctas_per_sm<T, VEC, KIND>();
+  const unsigned grid = static_cast<unsigned>(wanted < resident ? wanted : resident);
+  row_reduce_kernel<T, VEC, KIND><<<grid, 256, 0, stream>>>(p);
+  return launched();
+}
+
 template <typename T, bool VEC>
-int launch_row_reduce(int kind, const ReduceParams& p, unsigned grid, cudaStream_t stream) {
+int launch_row_reduce(int kind, const ReduceParams& p, int64_t wanted, int sm_count, cudaStream_t stream) {
   switch (kind) {
     case B200_REDUCE_ROW_SUM:
-      row_reduce_kernel<T, VEC, 0><<<grid, 256, 0, stream>>>(p);
-      break;
+      return launch_row_reduce_kind<T, VEC, 0>(p, wanted, sm_count, stream);
     case B200_REDUCE_ROW_DOT:
-      row_reduce_kernel<T, VEC, 1><<<grid, 256, 0, stream>>>(p);
-      break;
+      return launch_row_reduce_kind<T, VEC, 1>(p, wanted, sm_count, stream);
     default:
-      row_reduce_kernel<T, VEC, 2><<<grid, 256, 0, stream>>>(p);
+      return launch_row_reduce_kind<T, VEC, 2>(p, wanted, sm_count, stream);
   }
-  return launched();
 }
 
 template <typename T>
@@ -128,9 +150,8 @@ int run_row_reduce(int kind, ReduceParams p, cudaStream_t stream) {
   p.tpr = tpr;
   const int rows_per_cta = 256 / tpr;
   const int64_t wanted = ceil_div(p.m, rows_per_cta);
-  const int64_t resident = static_cast<int64_t>(dev.sm_count) * 8;
-  const unsigned grid = static_cast<unsigned>(wanted < resident ? wanted : resident);
-  return vec ? launch_row_reduce<T, true>(kind, p, grid, stream) : launch_row_reduce<T, false>(kind, p, grid, stream);
+  return vec ? launch_row_reduce<T, true>(kind, p, wanted, dev.sm_count, stream)
+             : launch_row_reduce<T, false>(kind, p, wanted, dev.sm_count, stream);
 }
 
 // ---------------------------------------------------------------------------
