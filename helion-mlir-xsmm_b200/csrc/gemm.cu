@@ -57,6 +57,28 @@ struct Resolved {
 };
 
 // Whether the f32 GEMM `d` can run as a widened bf16 GEMM (layouts TMA can describe).
+// K chunks of the widened product. At least one per kSplitChunkK elements; when the
+// chunks run as parallel work items (few output tiles), as many more as there are idle
+// CTA pairs for, so that each chunk is shorter (1024^3: 16 tiles x 4 chunks of 1536 on
+// 74 pairs instead of 3 of 2048). Shorter chunks only make the f32 sum more exact.
+int64_t split_chunk_count(const b200_gemm_desc& d, bool* parallel) {
+  const int64_t wide_k = d.k * kSplitTerms;
+  int64_t chunks = ceil_div(wide_k, kSplitChunkK);
+  const int64_t pair_tiles = ceil_div(d.m, 256) * ceil_div(d.n, 256);
+  const int64_t pairs = device_info().sm_count / 2;
+  *parallel = chunks > 1 && pair_tiles * chunks <= pairs;
+  if (*parallel) {
+    const int64_t room = pairs / pair_tiles;
+    for (int64_t c = room; c > chunks; --c) {
+      if (wide_k % (c * 64) == 0 && wide_k / c >= 512) {
+        chunks = c;
+        break;
+      }
+    }
+  }
+  return chunks;
+}
+
 bool f32_split_applies(const b200_gemm_desc& d) {
   if (d.dtype != B200_F32 || d.a_layout > B200_LAYOUT_COL || d.b_layout > B200_LAYOUT_COL) return false;
   if (d.batch != 1 || d.split_k > 1 || d.k < 1 || d.k > kSplitMaxK) return false;
@@ -147,11 +169,9 @@ int validate(const b200_gemm_desc* d, Resolved* r) {
     // Few output tiles: the K chunks of the widened product (added in f32 either way, in
     // the same order) run as parallel work items into partial sums, so that the chunks of
     // one tile occupy several SMs instead of running back to back on one.
-    const int64_t chunks = ceil_div(d->k * kSplitTerms, kSplitChunkK);
-    const int64_t pair_tiles = ceil_div(d->m, 256) * ceil_div(d->n, 256);
-    const int64_t pairs = device_info().sm_count / 2;
-    if (chunks > 1 && pair_tiles * chunks <= pairs)
-      r->split_partial_bytes = static_cast<size_t>(round_up(chunks * d->m * d->n * 4, 256));
+    bool parallel = false;
+    const int64_t chunks = split_chunk_count(*d, &parallel);
+    if (parallel) r->split_partial_bytes = static_cast<size_t>(round_up(chunks * d->m * d->n * 4, 256));
   }
   return 0;
 }
@@ -187,7 +207,8 @@ b200_gemm_desc split_desc(const b200_gemm_desc& d, void* a_wide, void* b_wide) {
   u.lda = d.a_layout == B200_LAYOUT_ROW ? u.k : d.m;  // [M, 6K] or [6K, M]
   u.ldb = d.b_layout == B200_LAYOUT_COL ? u.k : d.n;  // [N, 6K] or [6K, N]
   // chunks of the widened K are added in f32 by the epilogue (needs an f32 result)
-  u.split_k = static_cast<int32_t>(ceil_div(u.k, kSplitChunkK));
+  bool parallel = false;
+  u.split_k = static_cast<int32_t>(split_chunk_count(d, &parallel));
   if (u.split_k < 2) u.split_k = 0;
   u.workspace = nullptr;
   u.workspace_bytes = 0;

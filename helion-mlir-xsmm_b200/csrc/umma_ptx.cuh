@@ -43,20 +43,30 @@ __device__ __forceinline__ unsigned long long global_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+constexpr uint32_t kSpinsBeforeClock = 4096;
+
 // Waits for the phase of `parity` to complete. Gives up when the CTA aborted or
 // after kWaitBudgetNs; returns false then (and raises the abort with `code`).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
                                           int code, unsigned long long budget_ns = kWaitBudgetNs) {
   if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long start = global_ns();
+  // The wall clock (%globaltimer, slow to read) is only consulted once a wait has lasted
+  // for kSpinsBeforeClock more tries: ordinary waits, of a microsecond or a few, never pay
+  // for a read of it, and the budget starts a little late, which does not matter to a
+  // limit of seconds.
+  unsigned long long start = 0;
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((spin & 63u) == 0) {
       if (*abort_flag) return false;
-      if (global_ns() - start > budget_ns) {
-        *abort_flag = 1;
-        if (status) atomicOr(status, code);
-        return false;
+      if (spin >= kSpinsBeforeClock) {
+        const unsigned long long now = global_ns();
+        if (start == 0) start = now;
+        if (now - start > budget_ns) {
+          *abort_flag = 1;
+          if (status) atomicOr(status, code);
+          return false;
+        }
       }
     }
   }
