@@ -585,6 +585,17 @@ UmmaPlan umma_plan(const b200_gemm_desc& d, int sm_count, bool parallel_splits) 
   while (!fixed_n && bn > 64 &&
          ceil_div(d.m, kBlockM) * ceil_div(d.n, bn) * d.batch * psplit_factor * 8 < sm_count)
     bn = static_cast<int>(round_up(bn / 2, gran));
+  // Short K and less than half a round of 128x256 tiles: what the call costs is the fixed
+  // time of one tile (first copies, epilogue of the whole tile), not tensor throughput, so
+  // tiles narrow until they occupy the SMs (1024^3: 14.9 -> 12.2 us with 128 tiles of
+  // 128x64; 2048x512x1024: 14.4 -> 11.8 us).
+  if (!fixed_n && d.k <= 1024 && d.split_k <= 1) {
+    const int64_t row_tiles = ceil_div(d.m, kBlockM) * d.batch;
+    if (row_tiles * ceil_div(d.n, bn) * 2 <= sm_count) {
+      while (bn > 64 && row_tiles * ceil_div(d.n, static_cast<int>(round_up(bn / 2, gran))) <= sm_count)
+        bn = static_cast<int>(round_up(bn / 2, gran));
+    }
+  }
   plan.block_n = bn;
   const int want_splits = d.split_k > 1 ? d.split_k : 1;
   plan.psplits = parallel_splits ? want_splits : 1;
