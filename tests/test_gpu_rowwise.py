@@ -17,7 +17,9 @@ from oracle import ops as ref
 pytestmark = pytest.mark.gpu
 BF16, F32 = torch.bfloat16, torch.float32
 SHAPES = [(32, 128), (64, 256), (16, 129), (33, 257), (2, 65), (1, 127), (5, 2), (7, 1), (3, 4096), (9, 4100),
-          (4, 8192), (3, 10000), (2, 40000), (300, 64), (1000, 24)]
+          (4, 8192), (3, 10000), (2, 40000), (300, 64), (1000, 24),
+          # 512 threads per row: 32 values each (f32 and bf16), 64 each (bf16 only; f32 takes two passes)
+          (3, 16384), (2, 20000), (3, 32768), (2, 24584)]
 
 
 @pytest.fixture(scope="module")
@@ -59,7 +61,8 @@ def test_softmax_special_rows(ops) -> None:
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
-@pytest.mark.parametrize("shape", [(8, 96, 4), (33, 130, 1), (5, 4096, 1), (4, 4100, 1), (6, 768, 12), (2, 40000, 1), (3, 20000, 2)])
+@pytest.mark.parametrize("shape", [(8, 96, 4), (33, 130, 1), (5, 4096, 1), (4, 4100, 1), (6, 768, 12), (2, 40000, 1), (3, 20000, 2),
+                                   (2, 16384, 1), (2, 32768, 1), (2, 24584, 1), (2, 65536, 2)])
 def test_group_norm(ops, shape, dtype) -> None:
     m, c, groups = shape
     gen = torch.Generator().manual_seed(m + c + groups)
@@ -94,7 +97,7 @@ def test_group_norm_epilogues(ops) -> None:
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
-@pytest.mark.parametrize("shape", [(8, 96), (33, 130), (5, 4096), (2, 40000)])
+@pytest.mark.parametrize("shape", [(8, 96), (33, 130), (5, 4096), (2, 40000), (3, 16384), (2, 32768), (2, 20008)])
 def test_rms_norm(ops, shape, dtype) -> None:
     gen = torch.Generator().manual_seed(sum(shape))
     x = (torch.randn(*shape, generator=gen) * 2).to(dtype)
