@@ -1,6 +1,8 @@
-"""Benchmark of the hot path: the fused bf16 linear  y = GELU(x @ W^T + b).
+"""Benchmark of the hot path: the fused bf16 linear  y = GELU(x @ W^T + b), with the
+other four configurations of the baseline timed beside it in the same line.
 
-    python bench.py --gpus N --steps K --warmup W [--workload c2|c4|c1|c3|c5|attn] [--impl reference]
+    python bench.py --gpus N --steps K --warmup W [--workload c2|c4|c1|c3|c5|attn|c2n]
+                    [--only-main] [--impl reference]
 
 A step is one pass of the hot path over one batch of synthetic input. The default
 workload is the configuration the headline metric is quoted on: x [8192,4096],
@@ -9,11 +11,20 @@ rank runs its own batch of 8192 rows (rows are independent: no collective on the
 data path) and `value` is the whole-job TFLOP/s over the slowest rank's time.
 
 One JSON line is printed by rank 0. Besides the driver's keys it carries
-`roofline` (algorithmic FLOPs or bytes over the CUDA-event time of the dominant
-kernel, against the measured peak), `cpu_baseline` (the CPU restatement of the
-reference's operator timed on this host's cores on a bounded sample) and `e2e`
-(the same metric through the public operator with host buffers: pinned host ->
-device copy of x, the kernel, device -> host copy of y, every step).
+  roofline      algorithmic FLOPs or bytes over the CUDA-event time of the dominant
+                kernel, against the measured peak
+  cpu_baseline  the CPU restatement of the reference's operator timed on this host's
+                cores on a bounded sample
+  e2e           the same metric through the public operator with host buffers: pinned
+                host -> device copy of x, the kernel, device -> host copy of y, every step
+  parity_*      the result of one step on the same seeded tensors against the CPU
+                oracle, on samples, outside the timed region
+  sustained     the same step back to back for two seconds (the K-step figure of a
+                short run is a burst figure), against the measured sustained peak
+  linear_entry  the same step entered through linear(x, layer, F.gelu, cache)
+  configs       one block per other configuration (C1, C3, C4, C5), each timed for a
+                few hundred milliseconds of device time by an inner repeat count that
+                does not depend on --steps, with its own roofline, parity and clocks
 
 `--impl reference` times the CPU implementation of the path instead (the
 reference's own pipeline needs Helion + an MLIR toolchain, which are not
@@ -24,6 +35,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 from pathlib import Path
 import statistics
@@ -42,6 +54,8 @@ import torch.nn.functional as F  # noqa: E402
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 L2_BYTES = 126 * 1024 * 1024
+BLOCK_TARGET_MS = 300.0  # device time each configuration block is timed for
+SUSTAINED_SECONDS = 2.0
 
 
 def measured_peaks() -> tuple[dict[str, float], str]:
@@ -56,17 +70,19 @@ def measured_peaks() -> tuple[dict[str, float], str]:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi for the whole run; a timed
+    region asks for the samples that arrived inside its window."""
 
     QUERY = (
         "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
     )
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, device_index: int) -> None:
         self.device_index = device_index
-        self.lines: list[str] = []
+        self.lines: list[tuple[float, str]] = []
         self.proc: subprocess.Popen | None = None
         self.thread: threading.Thread | None = None
 
@@ -84,12 +100,12 @@ class ClockSampler:
         def pump() -> None:
             assert self.proc is not None and self.proc.stdout is not None
             for line in self.proc.stdout:
-                self.lines.append(line.strip())
+                self.lines.append((time.monotonic(), line.strip()))
 
         self.thread = threading.Thread(target=pump, daemon=True)
         self.thread.start()
 
-    def stop(self) -> dict[str, object]:
+    def stop(self) -> None:
         if self.proc is not None:
             self.proc.terminate()
             try:
@@ -98,23 +114,30 @@ class ClockSampler:
                 self.proc.kill()
         if self.thread is not None:
             self.thread.join(timeout=5)
-        clocks, max_clock, reasons = [], None, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+
+    def window(self, t0: float, t1: float) -> dict[str, object]:
+        """Clocks seen between ``t0`` and ``t1`` (time.monotonic); a sample is the state at the
+        moment nvidia-smi printed it, so the window is widened by one period at its end."""
+        clocks, power, max_clock, reasons = [], [], None, set()
+        for stamp, line in list(self.lines):
+            if stamp < t0 or stamp > t1 + 0.1:
+                continue
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 9:
                 continue
             try:
                 clocks.append(float(parts[1]))
                 max_clock = float(parts[2])
+                power.append(float(parts[3]))
             except ValueError:
                 continue
-            for name, value in zip(names, parts[5:9]):
+            for name, value in zip(self.NAMES, parts[5:9]):
                 if value.lower().startswith("active"):
                     reasons.add(name)
         return {
             "sm_mhz": statistics.median(clocks) if clocks else None,
             "sm_max_mhz": max_clock,
+            "power_w": max(power) if power else None,
             "reasons": sorted(reasons),
             "samples": len(clocks),
         }
@@ -124,13 +147,15 @@ class ClockSampler:
 
 
 class Workload:
-    """One benchmark configuration: device buffers, the step, its algorithmic work."""
+    """One benchmark configuration: device buffers, the step, its algorithmic work,
+    the parity check of one step, and the CPU restatement of the same step."""
 
     name = ""
     metric = ""
     unit = ""
     dtype = ""
     bound = "tensor"
+    traffic: float | None = None  # DRAM bytes per launch of the dominant kernel (ncu, profiles/)
 
     def setup(self, device: torch.device, rank: int) -> None:
         raise NotImplementedError
@@ -138,8 +163,10 @@ class Workload:
     def step(self, index: int) -> torch.Tensor:
         raise NotImplementedError
 
-    def e2e_step(self, index: int) -> tuple[int, int]:
-        raise NotImplementedError
+    def e2e_step(self, index: int) -> tuple[int, int] | None:
+        """One step through host buffers; returns (h2d bytes, d2h bytes), or None when the
+        workload has no host-buffer leg."""
+        return None
 
     def work_per_step(self) -> float:
         """FLOPs (tensor-bound) or bytes (HBM-bound) of one step on one GPU."""
@@ -148,9 +175,21 @@ class Workload:
     def config(self) -> dict[str, object]:
         raise NotImplementedError
 
-    def cpu_sample(self, threads: int) -> tuple[float, str]:
-        """Seconds per unit of work measure on the CPU port: returns (value in `unit`, description)."""
+    def parity(self) -> dict[str, object]:
+        """One step on the seeded tensors against the CPU oracle (sampled)."""
         raise NotImplementedError
+
+    def cpu_setup(self) -> str:
+        """Host tensors of a bounded sample of the workload; returns its description."""
+        raise NotImplementedError
+
+    def cpu_step(self) -> float:
+        """Runs the CPU restatement on the sample; returns the work done (FLOPs or bytes)."""
+        raise NotImplementedError
+
+    def launches_per_step(self) -> int | None:
+        """Kernels per step when they do not pass the library's launch counter (graph replays)."""
+        return None
 
 
 def _rotating(count: int, make):
@@ -162,6 +201,8 @@ class LinearGelu(Workload):
 
     name, metric, unit, dtype, bound = "c2_linear_gelu_8192x4096x4096", "bf16 GEMM TFLOP/s", "TFLOP/s", "bf16", "tensor"
     M, N, K, SETS = 8192, 4096, 4096, 3
+    traffic = 158.1e6  # gemm_umma_bf16_kernel<2>: 111.7 MB read + 46.5 MB written (algorithmic 167.8 MB)
+    via_linear = False
 
     def setup(self, device: torch.device, rank: int) -> None:
         import helion_mlir_utils as ops
@@ -175,9 +216,21 @@ class LinearGelu(Workload):
         self.xs = _rotating(self.SETS, lambda i: data["x"].roll(i, 0).to(device))
         self.x_pinned = data["x"].pin_memory()
         self.y_pinned = torch.empty(self.M, self.N, dtype=torch.bfloat16).pin_memory()
+        self.layer = torch.nn.Linear(self.K, self.N, dtype=torch.bfloat16, device=device)
+        with torch.no_grad():
+            self.layer.weight.copy_(self.w)
+            self.layer.bias.copy_(self.b)
+        self.cache = None
 
     def step(self, index: int) -> torch.Tensor:
+        if self.via_linear:
+            return self.linear_step(index)
         return self.ops.matmul(self.xs[index % self.SETS], self.w, trans_b=True, bias=self.b, epilogue=F.gelu)
+
+    def linear_step(self, index: int) -> torch.Tensor:
+        """The reference's stock entry for this configuration: linear() with the weight cache."""
+        y, self.cache = self.ops.linear(self.xs[index % self.SETS], self.layer, F.gelu, self.cache)
+        return y
 
     def e2e_step(self, index: int) -> tuple[int, int]:
         # Host rows in, host rows out (b200_gemm_host_rows): copy-in, GEMM and copy-out
@@ -192,22 +245,32 @@ class LinearGelu(Workload):
         return {
             "workload": self.name, "m_per_gpu": self.M, "n": self.N, "k": self.K, "epilogue": "bias+gelu_erf",
             "accumulate": "f32", "out": "bf16", "sharding": "rows (M) per GPU, no collective",
+            "entry": "linear(x, layer, F.gelu, cache)" if self.via_linear else "matmul(x, W, trans_b=True, bias=b, epilogue=F.gelu)",
             "l2": f"inputs rotated over {self.SETS} buffer sets (403 MB) > 126 MB L2",
         }
 
-    def cpu_sample(self, threads: int) -> tuple[float, str]:
+    def parity(self) -> dict[str, object]:
+        from oracle import sampled
+
+        rows = sampled.rows_of_interest(self.M, extra=4)
+        y = self.step(0)
+        return sampled.c2_rows(self.host["x"], self.host["w"], self.host["b"], y[rows.to(self.device)], rows)
+
+    CPU_ROWS = 1024
+
+    def cpu_setup(self) -> str:
+        from oracle import inputs
+
+        data = getattr(self, "host", None) or inputs.c2_linear(self.CPU_ROWS, self.N, self.K)
+        self.cpu = (data["x"][: self.CPU_ROWS].contiguous(), data["w"], data["b"])
+        return f"{self.CPU_ROWS} of {self.M} rows per step, f32-accumulate torch CPU restatement"
+
+    def cpu_step(self) -> float:
         from oracle import ops as ref
 
-        rows = 1024
-        x, w, b = self.host["x"][:rows], self.host["w"], self.host["b"]
-        ref.matmul(x[:64], w, trans_b=True, bias=b, epilogue=F.gelu, acc_dtype=torch.float32)
-        times = []
-        for _ in range(3):
-            t0 = time.perf_counter()
-            ref.matmul(x, w, trans_b=True, bias=b, epilogue=F.gelu, acc_dtype=torch.float32)
-            times.append(time.perf_counter() - t0)
-        flops = 2.0 * rows * self.N * self.K
-        return flops / min(times) / 1e12, f"{rows} of {self.M} rows, f32-accumulate torch CPU restatement, best of 3"
+        x, w, b = self.cpu
+        ref.matmul(x, w, trans_b=True, bias=b, epilogue=F.gelu, acc_dtype=torch.float32)
+        return 2.0 * x.shape[0] * self.N * self.K
 
 
 class RowNorms(Workload):
@@ -215,6 +278,7 @@ class RowNorms(Workload):
 
     name, metric, unit, dtype, bound = "c4_softmax_layernorm_rmsnorm_32768x4096", "softmax/norm HBM GB/s", "GB/s", "f32+bf16", "hbm"
     M, N = 32768, 4096
+    traffic = 860.1e6  # f32 softmax, scaled x4 from the 8192-row capture (134.26 MB read + 80.77 MB written)
 
     def setup(self, device: torch.device, rank: int) -> None:
         import helion_mlir_utils as ops
@@ -230,14 +294,22 @@ class RowNorms(Workload):
         self.x_pinned = data["x"].pin_memory()
         self.y_pinned = torch.empty(self.M, self.N).pin_memory()
 
-    def step(self, index: int) -> torch.Tensor:
+    def kernels(self):
         ops = self.ops
-        ops.softmax(self.x32)
-        ops.layer_norm(self.x32, self.g32, self.b32, 1e-5)
-        ops.rms_norm(self.x32, self.g32, 1e-5)
-        ops.softmax(self.x16)
-        ops.layer_norm(self.x16, self.g16, self.b16, 1e-5)
-        return ops.rms_norm(self.x16, self.g16, 1e-5)
+        return [
+            ("softmax_f32", 4, lambda: ops.softmax(self.x32)),
+            ("layer_norm_f32", 4, lambda: ops.layer_norm(self.x32, self.g32, self.b32, 1e-5)),
+            ("rms_norm_f32", 4, lambda: ops.rms_norm(self.x32, self.g32, 1e-5)),
+            ("softmax_bf16", 2, lambda: ops.softmax(self.x16)),
+            ("layer_norm_bf16", 2, lambda: ops.layer_norm(self.x16, self.g16, self.b16, 1e-5)),
+            ("rms_norm_bf16", 2, lambda: ops.rms_norm(self.x16, self.g16, 1e-5)),
+        ]
+
+    def step(self, index: int) -> torch.Tensor:
+        out = None
+        for _, _, run in self.kernels():
+            out = run()
+        return out
 
     def e2e_step(self, index: int) -> tuple[int, int]:
         self.ops.stream_rows(self.ops.softmax, self.x_pinned, self.y_pinned)
@@ -255,27 +327,44 @@ class RowNorms(Workload):
             "e2e": "softmax f32 only",
         }
 
-    def cpu_sample(self, threads: int) -> tuple[float, str]:
-        rows = 4096
-        x = self.host["x"][:rows]
-        g, b = self.host["gamma"], self.host["beta"]
-        xb = x.bfloat16()
+    def parity(self) -> dict[str, object]:
+        from oracle import sampled
 
-        def run() -> None:
-            for t, gg, bb in ((x, g, b), (xb, g.bfloat16(), b.bfloat16())):
-                tf = t.float()
-                torch.softmax(tf, -1).to(t.dtype)
-                F.layer_norm(tf, (self.N,), gg.float(), bb.float(), 1e-5).to(t.dtype)
-                F.rms_norm(tf, (self.N,), gg.float(), 1e-5).to(t.dtype)
+        ops = self.ops
+        rows = sampled.rows_of_interest(self.M, tile_rows=148, group_tiles=64, extra=24)
+        pick = rows.to(self.device)
+        reports = []
+        for x, g, b in ((self.x32, self.g32, self.b32), (self.x16, self.g16, self.b16)):
+            soft = ops.softmax(x)
+            run = {
+                "softmax": soft[pick],
+                "layer_norm": ops.layer_norm(x, g, b, 1e-5)[pick],
+                "rms_norm": ops.rms_norm(x, g, 1e-5)[pick],
+                "chained": ops.layer_norm(soft, g, b, 1e-5)[pick],
+            }
+            del soft
+            reports.append(sampled.c4_rows(x[pick].cpu(), g.cpu(), b.cpu(), run, self.M))
+        return sampled.worst(reports)
 
-        run()
-        times = []
-        for _ in range(3):
-            t0 = time.perf_counter()
-            run()
-            times.append(time.perf_counter() - t0)
-        moved = 3 * 2.0 * rows * self.N * 4 + 3 * 2.0 * rows * self.N * 2
-        return moved / min(times) / 1e9, f"{rows} of {self.M} rows, f32-compute torch CPU restatement, best of 3"
+    CPU_ROWS = 4096
+
+    def cpu_setup(self) -> str:
+        from oracle import inputs
+
+        data = getattr(self, "host", None) or inputs.c4_rows(self.CPU_ROWS, self.N)
+        x = data["x"][: self.CPU_ROWS].contiguous()
+        g, b = data["gamma"], data["beta"]
+        self.cpu = ((x, g, b), (x.bfloat16(), g.bfloat16(), b.bfloat16()))
+        return f"{self.CPU_ROWS} of {self.M} rows per step, six kernels, f32-compute torch CPU restatement"
+
+    def cpu_step(self) -> float:
+        for t, gg, bb in self.cpu:
+            tf = t.float()
+            torch.softmax(tf, -1).to(t.dtype)
+            F.layer_norm(tf, (self.N,), gg.float(), bb.float(), 1e-5).to(t.dtype)
+            F.rms_norm(tf, (self.N,), gg.float(), 1e-5).to(t.dtype)
+        rows = self.cpu[0][0].shape[0]
+        return 3 * 2.0 * rows * self.N * 4 + 3 * 2.0 * rows * self.N * 2
 
 
 class F32Matmul(Workload):
@@ -288,7 +377,7 @@ class F32Matmul(Workload):
         import helion_mlir_utils as ops
         from oracle import inputs
 
-        self.ops = ops
+        self.ops, self.device = ops, device
         data = inputs.c1_f32_matmul(self.SIZE)
         self.host = data
         # 12 rotating (A, B) pairs = 101 MB + outputs: beyond L2 together with the results.
@@ -298,18 +387,18 @@ class F32Matmul(Workload):
         self.c_pinned = torch.empty(self.SIZE, self.SIZE).pin_memory()
         self.a_stage, self.b_stage = torch.empty_like(self.a[0]), torch.empty_like(self.b[0])
 
-        # The call is three short kernels (two operand splits and the GEMM): replayed as
-        # one CUDA graph per operand pair, which takes the host out of the timed loop.
+        # The call is a few short kernels (operand splits, the GEMM, the ordered sum of its K
+        # chunks): replayed as one CUDA graph per operand pair, which takes the host out of the loop.
         from helion_mlir_backend import graphed
 
         self.calls = [graphed(lambda a, b: ops.matmul(a, b, block_sizes=(64, 64, 64)), a, b)
                       for a, b in zip(self.a, self.b)]
-        self.graph_launches = 0
 
     def step(self, index: int) -> torch.Tensor:
-        call = self.calls[index % self.SETS]
-        self.graph_launches += call.kernels  # replays do not pass the library's launch counter
-        return call()
+        return self.calls[index % self.SETS]()
+
+    def launches_per_step(self) -> int:
+        return self.calls[0].kernels
 
     def e2e_step(self, index: int) -> tuple[int, int]:
         self.a_stage.copy_(self.a_pinned, non_blocking=True)
@@ -322,18 +411,26 @@ class F32Matmul(Workload):
 
     def config(self) -> dict[str, object]:
         return {"workload": self.name, "block_sizes": [64, 64, 64], "sharding": "replicas only",
-                "launch": "one CUDA graph replay per call (split A, split B, GEMM)",
+                "launch": f"one CUDA graph replay per call ({self.calls[0].kernels} kernels)" if hasattr(self, "calls") else "one CUDA graph replay per call",
                 "l2": f"{self.SETS} rotating operand pairs (101 MB) plus outputs > 126 MB L2"}
 
-    def cpu_sample(self, threads: int) -> tuple[float, str]:
-        a, b = self.host["a"], self.host["b"]
+    def parity(self) -> dict[str, object]:
+        from oracle import sampled
+
+        out = self.calls[0]()  # the replayed graph is what is timed
+        return sampled.c1_whole(self.host["a"], self.host["b"], out)
+
+    def cpu_setup(self) -> str:
+        from oracle import inputs
+
+        data = getattr(self, "host", None) or inputs.c1_f32_matmul(self.SIZE)
+        self.cpu = (data["a"], data["b"])
+        return "the full 1024^3 f32 torch CPU matmul per step"
+
+    def cpu_step(self) -> float:
+        a, b = self.cpu
         a @ b
-        times = []
-        for _ in range(5):
-            t0 = time.perf_counter()
-            a @ b
-            times.append(time.perf_counter() - t0)
-        return 2.0 * self.SIZE**3 / min(times) / 1e12, "full 1024^3 f32 torch CPU matmul, best of 5"
+        return 2.0 * self.SIZE**3
 
 
 class BlockedMatmul(Workload):
@@ -341,14 +438,16 @@ class BlockedMatmul(Workload):
 
     name, metric, unit, dtype, bound = "c3_blocked_vnni_matmul_8192", "bf16 GEMM TFLOP/s", "TFLOP/s", "bf16", "tensor"
     SIZE = 8192
+    traffic = 1509.7e6  # gemm_umma_bf16_kernel<2> of the step: 1256 MB read + 253.7 MB written
 
     def setup(self, device: torch.device, rank: int) -> None:
         import helion_mlir_utils as ops
+        from oracle import inputs
 
-        self.ops = ops
-        gen = torch.Generator(device="cpu").manual_seed(1003 + rank)
-        a = torch.randn(self.SIZE, self.SIZE, generator=gen).bfloat16().to(device)
-        b = torch.randn(self.SIZE, self.SIZE, generator=gen).bfloat16().to(device)
+        self.ops, self.device = ops, device
+        data = inputs.c3_blocked(self.SIZE)
+        self.host = data
+        a, b = data["a"].to(device), data["b"].to(device)
         self.a4 = ops.pack_a_blocked(a)
         self.b5 = ops.pack_b_blocked_vnni(b)
         del a, b
@@ -357,23 +456,33 @@ class BlockedMatmul(Workload):
         s = self.SIZE
         return self.ops.matmul_blocked(self.a4, self.b5, s, s, s, out_dtype=torch.float32)
 
-    def e2e_step(self, index: int) -> tuple[int, int]:
-        self.step(index)
-        return 0, 0
-
     def work_per_step(self) -> float:
         return 2.0 * self.SIZE**3
 
     def config(self) -> dict[str, object]:
-        return {"workload": self.name, "out": "f32", "l2": "operands 268 MB + output 268 MB > 126 MB L2"}
+        return {"workload": self.name, "out": "f32", "sharding": "block rows of A per GPU, no collective",
+                "l2": "operands 268 MB + output 268 MB > 126 MB L2"}
 
-    def cpu_sample(self, threads: int) -> tuple[float, str]:
-        rows = 1024
-        a = torch.randn(rows, self.SIZE).bfloat16().float()
-        b = torch.randn(self.SIZE, self.SIZE).bfloat16().float()
-        t0 = time.perf_counter()
+    def parity(self) -> dict[str, object]:
+        from oracle import sampled
+
+        rows = sampled.rows_of_interest(self.SIZE, extra=8)
+        out = self.step(0)
+        return sampled.c3_rows(self.host["a"][rows], self.host["b"], out[rows.to(self.device)], self.SIZE)
+
+    CPU_ROWS = 1024
+
+    def cpu_setup(self) -> str:
+        from oracle import inputs
+
+        data = getattr(self, "host", None) or inputs.c3_blocked(self.SIZE)
+        self.cpu = (data["a"][: self.CPU_ROWS].float(), data["b"].float())
+        return f"{self.CPU_ROWS} of {self.SIZE} rows per step, torch CPU f32 matmul on unpacked operands"
+
+    def cpu_step(self) -> float:
+        a, b = self.cpu
         a @ b
-        return 2.0 * rows * self.SIZE**2 / (time.perf_counter() - t0) / 1e12, f"{rows} of {self.SIZE} rows, torch CPU f32 matmul on unpacked operands"
+        return 2.0 * a.shape[0] * self.SIZE**2
 
 
 class SplitKBmm(Workload):
@@ -381,11 +490,12 @@ class SplitKBmm(Workload):
 
     name, metric, unit, dtype, bound = "c5_split_k_bmm_64x512x512x16384", "bf16 GEMM TFLOP/s", "TFLOP/s", "bf16", "tensor"
     B, M, N, K = 64, 512, 512, 16384
+    traffic = 2216.6e6  # 37-batch capture (1258.5 MB read + 23.0 MB written) scaled to 64 batches
 
     def setup(self, device: torch.device, rank: int) -> None:
         import helion_mlir_utils as ops
 
-        self.ops = ops
+        self.ops, self.device = ops, device
         gen = torch.Generator(device=device).manual_seed(1005 + rank)
         self.a = (torch.rand(self.B, self.M, self.K, generator=gen, device=device) * 2 - 1).bfloat16()
         self.b = (torch.rand(self.B, self.K, self.N, generator=gen, device=device) * 2 - 1).bfloat16()
@@ -393,22 +503,36 @@ class SplitKBmm(Workload):
     def step(self, index: int) -> torch.Tensor:
         return self.ops.bmm(self.a, self.b, split_k=8, out_dtype=torch.float32)
 
-    def e2e_step(self, index: int) -> tuple[int, int]:
-        self.step(index)
-        return 0, 0
-
     def work_per_step(self) -> float:
         return 2.0 * self.B * self.M * self.N * self.K
 
-    def config(self) -> dict[str, object]:
-        return {"workload": self.name, "split_k": 8, "out": "f32", "l2": "operands 2.1 GB > 126 MB L2"}
+    def hbm_bytes_per_step(self) -> float:
+        return 2.0 * self.B * self.K * (self.M + self.N) + 4.0 * self.B * self.M * self.N
 
-    def cpu_sample(self, threads: int) -> tuple[float, str]:
-        a = (torch.rand(2, self.M, self.K) * 2 - 1).bfloat16().float()
-        b = (torch.rand(2, self.K, self.N) * 2 - 1).bfloat16().float()
-        t0 = time.perf_counter()
+    def config(self) -> dict[str, object]:
+        return {"workload": self.name, "split_k": 8, "out": "f32", "sharding": "batches per GPU, no collective",
+                "l2": "operands 2.1 GB > 126 MB L2"}
+
+    def parity(self) -> dict[str, object]:
+        from oracle import sampled
+
+        batches = sorted({0, self.B - 10, self.B - 9, self.B - 1} & set(range(self.B))) or [0]
+        out = self.step(0)
+        return sampled.c5_batches(self.a[batches].cpu(), self.b[batches].cpu(), out[batches], batches, self.B)
+
+    CPU_BATCHES = 2
+
+    def cpu_setup(self) -> str:
+        gen = torch.Generator().manual_seed(1005)
+        a = (torch.rand(self.CPU_BATCHES, self.M, self.K, generator=gen) * 2 - 1).bfloat16().float()
+        b = (torch.rand(self.CPU_BATCHES, self.K, self.N, generator=gen) * 2 - 1).bfloat16().float()
+        self.cpu = (a, b)
+        return f"{self.CPU_BATCHES} of {self.B} batches per step, torch CPU f32 bmm"
+
+    def cpu_step(self) -> float:
+        a, b = self.cpu
         torch.bmm(a, b)
-        return 2.0 * 2 * self.M * self.N * self.K / (time.perf_counter() - t0) / 1e12, "2 of 64 batches, torch CPU f32 bmm"
+        return 2.0 * a.shape[0] * self.M * self.N * self.K
 
 
 class Attention(Workload):
@@ -420,9 +544,10 @@ class Attention(Workload):
     def setup(self, device: torch.device, rank: int) -> None:
         import helion_mlir_utils as ops
 
-        self.ops = ops
+        self.ops, self.device = ops, device
         gen = torch.Generator().manual_seed(1006 + rank)
         host = [torch.randn(self.H, self.S, self.D, generator=gen).bfloat16() for _ in range(3)]
+        self.host = host
         # Two rotating operand sets: 2 x 4 x 134 MB, beyond the 126 MB L2.
         self.sets = _rotating(self.SETS, lambda i: [t.roll(i, 1).to(device) for t in host])
         self.pinned = [t.pin_memory() for t in host]
@@ -446,17 +571,31 @@ class Attention(Workload):
         return {"workload": self.name, "heads": self.H, "seq": self.S, "dim": self.D, "scale": "dim ** -0.5",
                 "sharding": "heads per GPU, no collective", "l2": "operands rotated over 2 sets (1.07 GB) > 126 MB L2"}
 
-    def cpu_sample(self, threads: int) -> tuple[float, str]:
+    def parity(self) -> dict[str, object]:
+        from oracle import ops as ref
+        from oracle import sampled
+
+        heads = [0, self.H - 1]
+        out = self.step(0)[heads]
+        q, k, v = (t[heads] for t in self.host)
+        expect = ref.attention(q, k, v, self.D ** -0.5)
+        return sampled._report(torch.bfloat16, out, expect, f"heads {heads} of {self.H}, whole")
+
+    CPU_HEADS = 2
+
+    def cpu_setup(self) -> str:
+        self.cpu = tuple(torch.randn(self.CPU_HEADS, self.S, self.D).bfloat16().float() for _ in range(3))
+        return f"{self.CPU_HEADS} of {self.H} heads per step, torch CPU restatement (f64 scores)"
+
+    def cpu_step(self) -> float:
         from oracle import ops as ref
 
-        heads = 2
-        q, k, v = (torch.randn(heads, self.S, self.D).bfloat16() for _ in range(3))
-        t0 = time.perf_counter()
-        ref.attention(q.float(), k.float(), v.float(), self.D ** -0.5)
-        return 4.0 * heads * self.S * self.S * self.D / (time.perf_counter() - t0) / 1e12, f"{heads} of {self.H} heads, torch CPU restatement (f64 scores)"
+        ref.attention(*self.cpu, self.D ** -0.5)
+        return 4.0 * self.CPU_HEADS * self.S * self.S * self.D
 
 
 WORKLOADS = {"c1": F32Matmul, "c2": LinearGelu, "c3": BlockedMatmul, "c4": RowNorms, "c5": SplitKBmm, "attn": Attention}
+BLOCKS = ["c4", "c1", "c3", "c5"]  # timed beside the main line, in this order
 
 
 # --------------------------------------------------------------------------- driver
@@ -469,44 +608,163 @@ def env_int(name: str, default: int) -> int:
         return default
 
 
+def cpu_baseline(workload: Workload, threads: int, budget_s: float = 6.0) -> dict[str, object]:
+    """The CPU restatement on a bounded sample: one warm-up step, then steps until
+    ``budget_s`` has passed (three at least); the rate is work over the median step."""
+    torch.set_num_threads(threads)
+    sample = workload.cpu_setup()
+    workload.cpu_step()
+    times, work = [], 0.0
+    t_end = time.perf_counter() + budget_s
+    while len(times) < 3 or (time.perf_counter() < t_end and len(times) < 50):
+        t0 = time.perf_counter()
+        work = workload.cpu_step()
+        times.append(time.perf_counter() - t0)
+    scale = 1e12 if workload.unit == "TFLOP/s" else 1e9
+    return {"value": work / statistics.median(times) / scale, "unit": workload.unit, "cores": threads, "kind": "port",
+            "sample": f"{sample}; median of {len(times)} steps"}
+
+
 def run_reference(args: argparse.Namespace, workload: Workload, rank: int) -> None:
-    """The CPU implementation of the path on this host's cores (rank 0 only)."""
+    """The CPU implementation of the path on this host's cores (rank 0 only): a step is
+    one run of the restatement on the bounded sample its description names."""
     if rank != 0:
         return
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
-    workload.host = None  # type: ignore[attr-defined]
-    # Host tensors only: build them without touching a device.
-    from oracle import inputs
-
-    if isinstance(workload, LinearGelu):
-        workload.host = inputs.c2_linear(1024, workload.N, workload.K)
-        workload.host["x"] = workload.host["x"]
-    elif isinstance(workload, RowNorms):
-        workload.host = inputs.c4_rows(4096, workload.N)
-    elif isinstance(workload, F32Matmul):
-        workload.host = inputs.c1_f32_matmul(workload.SIZE)
-    values = []
-    for _ in range(args.warmup):
-        workload.cpu_sample(threads)
-    t0 = time.perf_counter()
-    sample = ""
+    sample = workload.cpu_setup()
+    for _ in range(max(args.warmup, 1)):
+        workload.cpu_step()
+    times, work = [], 0.0
+    t_all = time.perf_counter()
     for _ in range(args.steps):
-        value, sample = workload.cpu_sample(threads)
-        values.append(value)
-    elapsed = time.perf_counter() - t0
-    value = statistics.median(values)
+        t0 = time.perf_counter()
+        work = workload.cpu_step()
+        times.append(time.perf_counter() - t0)
+    elapsed = time.perf_counter() - t_all
+    scale = 1e12 if workload.unit == "TFLOP/s" else 1e9
+    value = work * args.steps / elapsed / scale
     line = {
         "impl": "reference", "metric": workload.metric, "value": value, "unit": workload.unit, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * elapsed / max(args.steps, 1),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": workload.dtype, "data": "synthetic",
         "config": workload.config(),
-        "cpu_baseline": {"value": value, "unit": workload.unit, "cores": threads, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": workload.unit, "cores": threads, "kind": "port",
+                         "sample": f"{sample}; {args.steps} steps after {max(args.warmup, 1)} warm-up"},
         "e2e": {"value": value, "unit": workload.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
-        "note": "the reference's own pipeline needs Helion + MLIR/lighthouse (not installed): the CPU restatement under oracle/ is timed",
+        "note": "the reference's own pipeline needs Helion + MLIR/lighthouse (not installed): the CPU restatement under oracle/ is timed; a step is one run on the bounded sample, the rate is per unit of work",
     }
     print(json.dumps(line), flush=True)
+
+
+class Harness:
+    """Timing plumbing shared by the main line and the configuration blocks."""
+
+    def __init__(self, device: torch.device, rank: int, world: int, sampler: ClockSampler | None) -> None:
+        self.device, self.rank, self.world, self.sampler = device, rank, world, sampler
+        self.distributed = world > 1
+        self.peaks, self.peak_kind = measured_peaks()
+        self.start, self.stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def barrier(self) -> None:
+        if self.distributed:
+            import torch.distributed as dist
+
+            dist.barrier()
+        torch.cuda.synchronize(self.device)
+
+    def max_over_ranks(self, *values: float) -> list[float]:
+        t = torch.tensor(values, device=self.device, dtype=torch.float64)
+        if self.distributed:
+            import torch.distributed as dist
+
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [float(v) for v in t]
+
+    def timed(self, step, steps: int) -> tuple[float, dict[str, object], int]:
+        """``steps`` calls of ``step(i)`` between two events on the launch stream, a barrier and a
+        synchronise on both sides; returns (ms of the slowest rank, clocks in the window, launches)."""
+        from helion_mlir_backend import native
+
+        self.barrier()
+        before = native.counters()["launches"]
+        t0 = time.monotonic()
+        self.start.record()
+        for i in range(steps):
+            step(i)
+        self.stop.record()
+        self.barrier()
+        t1 = time.monotonic()
+        ms = self.max_over_ranks(self.start.elapsed_time(self.stop))[0]
+        clocks = self.sampler.window(t0, t1) if self.sampler is not None else {}
+        return ms, clocks, int(native.counters()["launches"] - before)
+
+    def roofline(self, workload: Workload, per_gpu: float) -> dict[str, object]:
+        if workload.bound == "tensor":
+            peak, unit, what = self.peaks["bf16_tflops"], "TFLOP/s", "burst cuBLAS bf16"
+        else:
+            peak, unit, what = self.peaks["hbm_gbs"], "GB/s", "copy bandwidth"
+        return {"bound": workload.bound, "achieved": per_gpu, "peak": peak, "unit": unit, "frac": per_gpu / peak,
+                "peak_source": f"{self.peak_kind} ({what})", "traffic": workload.traffic}
+
+
+def run_block(key: str, harness: Harness, rank: int, with_cpu: bool) -> dict[str, object]:
+    """One of the other configurations: set up, warm up, size the inner repeat count from a
+    pilot so that the timed region is BLOCK_TARGET_MS of device time, time it, check parity."""
+    workload: Workload = WORKLOADS[key]()
+    workload.setup(harness.device, rank)
+    for i in range(5):
+        workload.step(i)
+    pilot_ms, _, _ = harness.timed(workload.step, 10)
+    repeats = int(min(20000, max(20, math.ceil(BLOCK_TARGET_MS / max(pilot_ms / 10, 1e-3)))))
+    ms, clocks, launches = harness.timed(workload.step, repeats)
+    graph_kernels = workload.launches_per_step()
+    if graph_kernels is not None:
+        launches = graph_kernels * repeats
+    scale = 1e12 if workload.unit == "TFLOP/s" else 1e9
+    work = workload.work_per_step()
+    per_gpu = work * repeats / (ms * 1e-3) / scale
+    block: dict[str, object] = {
+        "metric": workload.metric, "value": per_gpu * harness.world, "unit": workload.unit, "per_gpu": per_gpu,
+        "ms_per_step": ms / repeats, "inner_repeats": repeats,
+        "timing": f"{repeats} steps back to back (sized for {BLOCK_TARGET_MS:.0f} ms of device time, independent of --steps), CUDA events, max over ranks",
+        "dtype": workload.dtype, "config": workload.config(), "roofline": harness.roofline(workload, per_gpu),
+        "gpu_launches": launches, "clocks": clocks,
+    }
+    if isinstance(workload, SplitKBmm):
+        gbs = workload.hbm_bytes_per_step() * repeats / (ms * 1e-3) / 1e9
+        block["roofline_hbm"] = {"bound": "hbm", "achieved": gbs, "peak": harness.peaks["hbm_gbs"], "unit": "GB/s",
+                                 "frac": gbs / harness.peaks["hbm_gbs"],
+                                 "note": "the configuration is bound by the larger of its two fractions"}
+    if isinstance(workload, RowNorms):
+        # each of the six kernels alone, 20 launches back to back
+        per_kernel = {}
+        for name, size, run in workload.kernels():
+            k_ms, _, _ = harness.timed(lambda i, run=run: run(), 20)
+            gbs = 2.0 * workload.M * workload.N * size * 20 / (k_ms * 1e-3) / 1e9
+            per_kernel[name] = {"GB/s": gbs, "frac": gbs / harness.peaks["hbm_gbs"]}
+        block["kernels"] = per_kernel
+        e2e = workload.e2e_step(0)
+        if e2e is not None:
+            e2e_ms, _, _ = harness.timed(workload.e2e_step, 5)
+            block["e2e"] = {"value": 2.0 * workload.M * workload.N * 4 * 5 * harness.world / (e2e_ms * 1e-3) / 1e9,
+                            "unit": "GB/s", "what": "stream_rows(softmax) f32 through pinned host buffers",
+                            "h2d_bytes_per_step": e2e[0], "d2h_bytes_per_step": e2e[1], "ms_per_step": e2e_ms / 5}
+    if rank == 0:
+        try:
+            block.update(workload.parity())
+        except Exception as exc:  # a parity leg that cannot run is a failed parity, not a crashed benchmark
+            block.update({"parity_metric": None, "parity_pass": False, "parity_error": f"{type(exc).__name__}: {exc}"})
+        if with_cpu:
+            block["cpu_baseline"] = cpu_baseline(workload, os.cpu_count() or 1, budget_s=3.0)
+    harness.barrier()
+    del workload
+    from helion_mlir_utils import host_io
+
+    host_io.release()
+    torch.cuda.empty_cache()
+    return block
 
 
 def main() -> None:
@@ -517,6 +775,8 @@ def main() -> None:
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     parser.add_argument("--rows", type=int, default=0, help="rows per GPU of the c2/c4 workloads, heads per GPU of attn, batches per GPU of c5 (default: the configuration's; smaller sizes are for profiler captures, not for reported numbers)")
+    parser.add_argument("--only-main", action="store_true", help="skip the blocks of the other configurations, the sustained leg and the linear() leg")
+    parser.add_argument("--via-linear", action="store_true", help="c2: time linear(x, layer, F.gelu, cache) as the main step")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-e2e", action="store_true")
     args = parser.parse_args()
@@ -530,6 +790,8 @@ def main() -> None:
             if hasattr(workload, name):
                 setattr(workload, name, args.rows)
                 break
+    if args.via_linear and isinstance(workload, LinearGelu):
+        workload.via_linear = True
     if args.impl == "reference":
         run_reference(args, workload, rank)
         return
@@ -548,104 +810,103 @@ def main() -> None:
 
     from helion_mlir_backend import native
 
-    workload.setup(device, rank)
-    peaks, peak_kind = measured_peaks()
-
-    def barrier() -> None:
-        if distributed:
-            dist.barrier()
-        torch.cuda.synchronize(device)
-
-    # The clock sampler covers warm-up and timed region (100 ms period: a timed region
-    # of a few milliseconds alone would see no sample); the warm-up is the same load.
-    sampler = ClockSampler(torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ else local_rank)
+    sampler = None
     if rank == 0:
+        sampler = ClockSampler(torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ else local_rank)
         sampler.start()
-        time.sleep(0.12)
+    harness = Harness(device, rank, world, sampler)
+    workload.setup(device, rank)
+
+    # The warm-up is the same load as the timed region and is inside the clock window: a
+    # timed region of a few milliseconds alone would see no 100 ms sample.
+    t_warm = time.monotonic()
+    time.sleep(0.12)
     for i in range(warmup):
         workload.step(i)
-    barrier()
-    launches_before = native.counters()["launches"]
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    graph_before = getattr(workload, "graph_launches", 0)
-    barrier()
-    start.record()
-    for i in range(args.steps):
-        workload.step(i)
-    stop.record()
-    barrier()
-    launches = native.counters()["launches"] - launches_before + getattr(workload, "graph_launches", 0) - graph_before
-    device_ms = start.elapsed_time(stop)
-    clocks = sampler.stop() if rank == 0 else {}
+    device_ms, clocks, launches = harness.timed(workload.step, args.steps)
+    if sampler is not None:
+        clocks = sampler.window(t_warm, time.monotonic())
+    graph_kernels = workload.launches_per_step()
+    if graph_kernels is not None:
+        launches = graph_kernels * args.steps
 
     e2e_ms, h2d, d2h = None, 0, 0
-    if not args.no_e2e:
-        for i in range(2):
-            workload.e2e_step(i)
-        barrier()
-        start.record()
-        for i in range(args.steps):
-            h2d, d2h = workload.e2e_step(i)
-        stop.record()
-        barrier()
-        e2e_ms = start.elapsed_time(stop)
+    first = None if args.no_e2e else workload.e2e_step(0)
+    if first is not None:
+        h2d, d2h = first
+        workload.e2e_step(1)
+        e2e_ms, _, _ = harness.timed(workload.e2e_step, args.steps)
+
+    main_only = args.only_main or args.workload != "c2"
+    extras: dict[str, object] = {}
+    if not main_only and isinstance(workload, LinearGelu):
+        # the same step back to back for SUSTAINED_SECONDS: the power-capped, steady figure
+        count = int(min(50000, max(args.steps, math.ceil(SUSTAINED_SECONDS * 1e3 / max(device_ms / args.steps, 1e-3)))))
+        s_ms, s_clocks, _ = harness.timed(workload.step, count)
+        s_per_gpu = workload.work_per_step() * count / (s_ms * 1e-3) / 1e12
+        extras["sustained"] = {
+            "value": s_per_gpu * world, "per_gpu": s_per_gpu, "unit": "TFLOP/s", "steps": count, "ms_per_step": s_ms / count,
+            "peak": harness.peaks["bf16_tflops_sustained"], "frac": s_per_gpu / harness.peaks["bf16_tflops_sustained"],
+            "peak_source": f"{harness.peak_kind} (cuBLAS bf16 back to back for seconds)", "clocks": s_clocks,
+        }
+        for i in range(3):
+            workload.linear_step(i)
+        l_ms, _, _ = harness.timed(workload.linear_step, args.steps)
+        l_per_gpu = workload.work_per_step() * args.steps / (l_ms * 1e-3) / 1e12
+        extras["linear_entry"] = {
+            "value": l_per_gpu * world, "unit": "TFLOP/s", "ms_per_step": l_ms / args.steps,
+            "entry": "linear(x, layer, F.gelu, cache): the weight cache's prepared call; `value` of the line is matmul(x, W, trans_b=True, bias=b, epilogue=F.gelu) unless --via-linear",
+        }
 
     status = native.kernel_status(device)
-    times = torch.tensor([device_ms, e2e_ms if e2e_ms is not None else 0.0], device=device, dtype=torch.float64)
-    if distributed:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    device_ms, e2e_max = float(times[0]), float(times[1])
+    parity: dict[str, object] = {}
+    if rank == 0:
+        try:
+            parity = workload.parity()
+        except Exception as exc:
+            parity = {"parity_metric": None, "parity_pass": False, "parity_error": f"{type(exc).__name__}: {exc}"}
+    harness.barrier()
 
+    blocks: dict[str, object] = {}
+    if not main_only:
+        del workload.xs
+        torch.cuda.empty_cache()
+        for key in BLOCKS:
+            blocks[key] = run_block(key, harness, rank, with_cpu=(world == 1 and not args.no_cpu_baseline and key == "c4"))
+        status |= native.kernel_status(device)
+
+    if sampler is not None:
+        sampler.stop()
     if rank == 0:
         scale = 1e12 if workload.unit == "TFLOP/s" else 1e9
         work = workload.work_per_step()
         value = work * args.steps * world / (device_ms * 1e-3) / scale
-        per_gpu = work * args.steps / (device_ms * 1e-3) / scale
-        if workload.bound == "tensor":
-            peak, peak_unit = peaks["bf16_tflops"], "TFLOP/s"
-        else:
-            peak, peak_unit = peaks["hbm_gbs"], "GB/s"
+        per_gpu = value / world
         line: dict[str, object] = {
             "metric": workload.metric, "value": value, "unit": workload.unit, "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": device_ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": workload.dtype, "data": "synthetic", "config": workload.config(),
-            "roofline": {
-                "bound": workload.bound, "achieved": per_gpu, "peak": peak, "unit": peak_unit, "frac": per_gpu / peak,
-                "peak_source": f"{peak_kind} ({'burst cuBLAS bf16' if workload.bound == 'tensor' else 'copy bandwidth'})",
-                "traffic": TRAFFIC.get(args.workload),
-            },
+            "roofline": harness.roofline(workload, per_gpu),
             "gpu_launches": int(launches),
             "clocks": clocks,
             "kernel_status": status,
         }
-        if e2e_ms is not None and h2d + d2h == 0:
-            # this workload has no host-buffer leg: say so instead of repeating the device-resident number
-            line["e2e"] = None
-        elif e2e_ms is not None:
+        line.update(parity)
+        if e2e_ms is not None:
             line["e2e"] = {
-                "value": work * args.steps * world / (e2e_max * 1e-3) / scale, "unit": workload.unit,
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_max / args.steps,
+                "value": work * args.steps * world / (e2e_ms * 1e-3) / scale, "unit": workload.unit,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps,
             }
+        else:
+            line["e2e"] = None  # this workload has no host-buffer leg
+        line.update(extras)
+        if blocks:
+            line["configs"] = blocks
         if not args.no_cpu_baseline and world == 1:
-            threads = os.cpu_count() or 1
-            torch.set_num_threads(threads)
-            cpu_value, sample = workload.cpu_sample(threads)
-            line["cpu_baseline"] = {"value": cpu_value, "unit": workload.unit, "cores": threads, "kind": "port", "sample": sample}
+            line["cpu_baseline"] = cpu_baseline(workload, os.cpu_count() or 1)
         print(json.dumps(line), flush=True)
     if distributed:
         dist.destroy_process_group()
-
-
-# DRAM bytes (read + write) per launch of each workload's dominant kernel, from
-# the ncu captures summarised under profiles/ (None until captured).
-TRAFFIC: dict[str, float | None] = {
-    "c1": None,
-    "c2": 158.1e6,  # gemm_umma_bf16_kernel<2>: 111.7 MB read + 46.5 MB written (algorithmic 167.8 MB)
-    "c3": 1509.7e6,  # gemm_umma_bf16_kernel<2> of the step: 1256 MB read + 253.7 MB written (operands streamed 4.7 times)
-    "c4": 860.1e6,  # f32 softmax, scaled x4 from the 8192-row capture (134.26 MB read + 80.77 MB written)
-    "c5": 2216.6e6,  # 37-batch capture (1258.5 MB read + 23.0 MB written) scaled to 64 batches
-    "attn": None,
-}
 
 
 if __name__ == "__main__":

@@ -10,7 +10,11 @@
 // two transfers; the GEMM hides behind them. The staging ring, the two copy
 // streams and the events belong to the library (one set per device) and persist
 // between calls, so back-to-back calls overlap too: the next call's copy-in does
-// not wait for the previous call's copy-out.
+// not wait for the previous call's copy-out, unless it reads host memory that an
+// earlier call's copy-out writes (a chained call: the result of one is the input
+// of the next). The copy-in stream is not ordered after other work of the caller's
+// stream: host rows that such work produces asynchronously must be complete, or the
+// caller must have synchronised, before the call is made.
 #include <mutex>
 
 #include "common.cuh"
@@ -31,7 +35,42 @@ struct Lanes {
   size_t staging_bytes = 0;
   size_t a_chunk = 0, c_chunk = 0;  // how the ring is carved at present
   uint64_t next = 0;  // chunks issued so far: slot = next % kDepth
+  // Host ranges that copy-outs of earlier calls write, newest last; ranges that fall
+  // out of the list are merged into `old_begin..old_end` (a superset: it can only
+  // cost an overlap, never miss one). `last_out`: slot of the newest copy-out.
+  static constexpr int kRanges = 8;
+  uintptr_t out_begin[kRanges] = {}, out_end[kRanges] = {};
+  int out_count = 0;
+  uintptr_t old_begin = 0, old_end = 0;
+  int last_out = -1;
 };
+
+bool reads_earlier_output(const Lanes& l, uintptr_t begin, uintptr_t end) {
+  if (l.old_begin < end && begin < l.old_end) return true;
+  for (int i = 0; i < l.out_count; ++i)
+    if (l.out_begin[i] < end && begin < l.out_end[i]) return true;
+  return false;
+}
+
+void remember_output(Lanes& l, uintptr_t begin, uintptr_t end) {
+  if (l.out_count == Lanes::kRanges) {
+    if (l.old_end == 0) {
+      l.old_begin = l.out_begin[0];
+      l.old_end = l.out_end[0];
+    } else {
+      if (l.out_begin[0] < l.old_begin) l.old_begin = l.out_begin[0];
+      if (l.out_end[0] > l.old_end) l.old_end = l.out_end[0];
+    }
+    for (int i = 1; i < Lanes::kRanges; ++i) {
+      l.out_begin[i - 1] = l.out_begin[i];
+      l.out_end[i - 1] = l.out_end[i];
+    }
+    --l.out_count;
+  }
+  l.out_begin[l.out_count] = begin;
+  l.out_end[l.out_count] = end;
+  ++l.out_count;
+}
 
 Lanes g_lanes[kMaxLaneDevices];
 std::mutex g_lanes_mutex;
@@ -131,6 +170,20 @@ extern "C" int b200_gemm_host_rows(const b200_gemm_desc* desc, const void* a_hos
     return finish(-static_cast<int>(err));
   }
 
+  // A chained call: these rows are (part of) what an earlier call's copy-out writes.
+  // The copy-out stream runs in order, so its newest event covers all earlier ones.
+  {
+    const uintptr_t a0 = reinterpret_cast<uintptr_t>(a_host);
+    const uintptr_t a1 = a0 + static_cast<uintptr_t>((d.m - 1) * a_row_bytes + d.k * static_cast<int64_t>(dtype_size(d.dtype)));
+    if (l.last_out >= 0 && reads_earlier_output(l, a0, a1)) {
+      err = cudaStreamWaitEvent(l.copy_in, l.copied_out[l.last_out], 0);
+      if (err != cudaSuccess) {
+        cudaGetLastError();
+        return finish(-static_cast<int>(err));
+      }
+    }
+  }
+
   int last_slots[kDepth];
   int issued = 0;
   int gemm_rc = 0;
@@ -164,7 +217,12 @@ extern "C" int b200_gemm_host_rows(const b200_gemm_desc* desc, const void* a_hos
     if (err == cudaSuccess) err = cudaEventRecord(l.copied_out[slot], l.copy_out);
     if (err != cudaSuccess) break;
     l.used[slot] = true;
+    l.last_out = slot;
     last_slots[issued % kDepth] = slot;
+  }
+  if (issued > 0) {
+    const uintptr_t c0 = reinterpret_cast<uintptr_t>(c_host);
+    remember_output(l, c0, c0 + static_cast<uintptr_t>((d.m - 1) * c_row_bytes + d.n * static_cast<int64_t>(dtype_size(d.out_dtype))));
   }
   // The caller's stream sees the host result: it waits for the copy-outs still in flight.
   const int tail = issued < kDepth ? issued : kDepth;
@@ -192,6 +250,10 @@ extern "C" int b200_host_rows_release(void) {
   l.staging = nullptr;
   l.staging_bytes = 0;
   for (bool& u : l.used) u = false;
+  // both copy streams are idle: no copy-out of an earlier call is in flight any more
+  l.out_count = 0;
+  l.old_begin = l.old_end = 0;
+  l.last_out = -1;
   cudaGetLastError();
   return 0;
 }

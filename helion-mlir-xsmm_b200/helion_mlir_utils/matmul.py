@@ -579,7 +579,13 @@ def matmul_host(
     out on three streams at once, so a call costs about the larger of the two PCIe
     transfers. Returns ``out_host`` (allocated pinned when not given) with
     everything enqueued: synchronise the current stream before reading it. The
-    epilogue must be one the kernel fuses (see ``epilogues.resolve``)."""
+    epilogue must be one the kernel fuses (see ``epilogues.resolve``).
+
+    ``a_host`` is read by a copy stream of the library that is ordered after
+    earlier ``matmul_host`` results (a call may take the ``out_host`` of an earlier
+    one as its ``a_host`` without a synchronisation in between) but not after other
+    work of the current stream: rows that such work writes asynchronously (a
+    non-blocking device-to-host copy, say) must be complete before this call."""
     if a_host.is_cuda or not b.is_cuda:
         raise ValueError("matmul_host() takes a host a_host and a device b")
     if a_host.dim() != 2 or b.dim() != 2 or a_host.dtype != b.dtype or a_host.dtype not in _SUPPORTED_DTYPES:

@@ -144,7 +144,12 @@ size_t b200_gemm_workspace_bytes(const b200_gemm_desc* desc);
  * be pinned (cudaHostAlloc / cudaHostRegister): pageable memory works but copies
  * synchronously. On return everything is enqueued; `stream` waits for the last
  * copy-out, so synchronising `stream` makes `c_host` readable. `a_host` must hold
- * its data when the call is made and stay unchanged until then. The first call on
+ * its data when the call is made and stay unchanged until then, with one
+ * exception: rows that an earlier b200_gemm_host_rows call on this device writes as
+ * its `c_host` (a chained call) need no synchronisation in between, the copy-in
+ * waits for that copy-out. The copy-in stream is NOT ordered after other work on
+ * `stream`: host rows produced by such work asynchronously must be complete (or
+ * `stream` synchronised) before the call. The first call on
  * a device creates the streams and allocates the ring (cudaMalloc); a later call
  * that needs a larger ring synchronises and reallocates. */
 int b200_gemm_host_rows(const b200_gemm_desc* desc, const void* a_host, void* c_host, int64_t chunk_rows,
