@@ -114,11 +114,11 @@ def test_chained_host_calls_read_the_first_result(ops) -> None:
     x = torch.randn(m, k, generator=gen).bfloat16().pin_memory()
     w1 = (torch.randn(n1, k, generator=gen) / 32).bfloat16().cuda()
     w2 = (torch.randn(n2, n1, generator=gen) / 32).bfloat16().cuda()
-    expect = ops.matmul(ops.matmul(x.cuda(), w1, trans_b=True, epilogue=torch.relu), w2, trans_b=True).cpu()
+    expect = ops.matmul(ops.matmul(x.cuda(), w1, trans_b=True, epilogue=torch.relu), w2, trans_b=True, epilogue=torch.relu).cpu()
     for round_ in range(3):  # the staging ring and the copy streams persist between rounds
         hidden = torch.full((m, n1), float("nan"), dtype=torch.bfloat16).pin_memory()
         out = torch.full((m, n2), float("nan"), dtype=torch.bfloat16).pin_memory()
         ops.matmul_host(x, w1, hidden, trans_b=True, epilogue=torch.relu, chunk_rows=512)
-        ops.matmul_host(hidden, w2, out, trans_b=True, chunk_rows=512)
+        ops.matmul_host(hidden, w2, out, trans_b=True, epilogue=torch.relu, chunk_rows=512)
         torch.cuda.current_stream().synchronize()
         assert torch.equal(out, expect), round_
