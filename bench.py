@@ -155,6 +155,7 @@ class Workload:
     unit = ""
     dtype = ""
     bound = "tensor"
+    scaling = "weak"  # per-GPU work is fixed as N grows ("strong": total work is fixed)
     traffic: float | None = None  # DRAM bytes per launch of the dominant kernel (ncu, profiles/)
 
     def setup(self, device: torch.device, rank: int) -> None:
@@ -594,7 +595,84 @@ class Attention(Workload):
         return 4.0 * self.CPU_HEADS * self.S * self.S * self.D
 
 
-WORKLOADS = {"c1": F32Matmul, "c2": LinearGelu, "c3": BlockedMatmul, "c4": RowNorms, "c5": SplitKBmm, "attn": Attention}
+class ColumnShardedLinear(Workload):
+    """C2-N: the C2 linear with W split along N over the ranks; every rank holds all of x,
+    computes its columns of y and the column shards are all-gathered (NCCL) into the whole
+    y on every rank. The total work is C2's whatever the number of GPUs (strong scaling)."""
+
+    name, metric, unit, dtype, bound = "c2n_column_sharded_linear_8192x4096x4096", "bf16 GEMM TFLOP/s", "TFLOP/s", "bf16", "tensor"
+    scaling = "strong"
+    M, N, K, SETS = 8192, 4096, 4096, 3
+    fused = False
+
+    def setup(self, device: torch.device, rank: int) -> None:
+        import torch.distributed as dist
+
+        import helion_mlir_utils as ops
+        from helion_mlir_utils import sharding
+        from oracle import inputs
+
+        self.ops, self.device, self.sharding = ops, device, sharding
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        if self.N % self.world:
+            raise SystemExit(f"c2n: {self.N} columns do not divide over {self.world} ranks")
+        data = inputs.c2_linear(self.M, self.N, self.K)  # the same x, W, b on every rank
+        self.host = data
+        n0, n1 = sharding.shard_bounds(self.N, self.world, self.rank)
+        self.w, self.b = data["w"][n0:n1].contiguous().to(device), data["b"][n0:n1].contiguous().to(device)
+        self.xs = _rotating(self.SETS, lambda i: data["x"].roll(i, 0).to(device))
+        self.fused_call = None
+        if self.fused:
+            self.fused_call = sharding.FusedColumnShardedLinear(self.M, self.N, self.K, torch.bfloat16, device)
+
+    def step(self, index: int) -> torch.Tensor:
+        x = self.xs[index % self.SETS]
+        if self.fused_call is not None:
+            return self.fused_call(x, self.w, self.b, F.gelu)
+        if self.world == 1:
+            return self.ops.matmul(x, self.w, trans_b=True, bias=self.b, epilogue=F.gelu)
+        return self.sharding.column_sharded_linear(x, self.w, self.b, self.N, F.gelu)
+
+    def gemm_only(self, index: int) -> torch.Tensor:
+        return self.ops.matmul(self.xs[index % self.SETS], self.w, trans_b=True, bias=self.b, epilogue=F.gelu)
+
+    def work_per_step(self) -> float:
+        return 2.0 * self.M * self.N * self.K / self.world
+
+    def config(self) -> dict[str, object]:
+        return {
+            "workload": self.name, "m": self.M, "n": self.N, "k": self.K, "epilogue": "bias+gelu_erf",
+            "sharding": f"W split along N over {getattr(self, 'world', 1)} ranks, x replicated",
+            "collective": ("epilogue stores into every rank's y over NVLink peer memory, then one flag per rank pair"
+                           if self.fused else "NCCL all-gather of the [M, N/G] column shards, then one strided copy"),
+            "l2": f"inputs rotated over {self.SETS} buffer sets",
+        }
+
+    def parity(self) -> dict[str, object]:
+        from oracle import sampled
+
+        rows = sampled.rows_of_interest(self.M, extra=4)
+        y = self.step(0)
+        torch.cuda.synchronize()
+        return sampled.c2_rows(self.host["x"], self.host["w"], self.host["b"], y[rows.to(self.device)], rows)
+
+    CPU_ROWS = 1024
+
+    def cpu_setup(self) -> str:
+        return LinearGelu.cpu_setup(self)  # the same arithmetic as C2
+
+    def cpu_step(self) -> float:
+        return LinearGelu.cpu_step(self)
+
+
+class FusedColumnShardedLinear(ColumnShardedLinear):
+    name = "c2n_fused_column_sharded_linear_8192x4096x4096"
+    fused = True
+
+
+WORKLOADS = {"c1": F32Matmul, "c2": LinearGelu, "c3": BlockedMatmul, "c4": RowNorms, "c5": SplitKBmm, "attn": Attention,
+             "c2n": ColumnShardedLinear, "c2n_fused": FusedColumnShardedLinear}
 BLOCKS = ["c4", "c1", "c3", "c5"]  # timed beside the main line, in this order
 
 
@@ -858,6 +936,14 @@ def main() -> None:
             "entry": "linear(x, layer, F.gelu, cache): the weight cache's prepared call; `value` of the line is matmul(x, W, trans_b=True, bias=b, epilogue=F.gelu) unless --via-linear",
         }
 
+    if isinstance(workload, ColumnShardedLinear):
+        # where the step's time goes: the local GEMM alone, and the rest (the exchange)
+        g_ms, _, _ = harness.timed(workload.gemm_only, args.steps)
+        extras["split"] = {"gemm_ms_per_step": g_ms / args.steps,
+                           "exchange_ms_per_step": max(device_ms - g_ms, 0.0) / args.steps,
+                           "exchange_share": max(device_ms - g_ms, 0.0) / device_ms,
+                           "note": "local GEMM of this rank's columns timed alone; the remainder of the step is the exchange"}
+
     status = native.kernel_status(device)
     parity: dict[str, object] = {}
     if rank == 0:
@@ -884,9 +970,9 @@ def main() -> None:
         per_gpu = value / world
         line: dict[str, object] = {
             "metric": workload.metric, "value": value, "unit": workload.unit, "n_gpus": world, "steps": args.steps,
-            "warmup": warmup, "ms_per_step": device_ms / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": workload.dtype, "data": "synthetic", "config": workload.config(),
-            "roofline": harness.roofline(workload, per_gpu),
+            "warmup": warmup, "ms_per_step": device_ms / args.steps, "higher_is_better": True,
+            "scaling": workload.scaling, "vs_baseline": None, "dtype": workload.dtype, "data": "synthetic",
+            "config": workload.config(), "roofline": harness.roofline(workload, per_gpu),
             "gpu_launches": int(launches),
             "clocks": clocks,
             "kernel_status": status,

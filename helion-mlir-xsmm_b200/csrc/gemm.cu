@@ -5,8 +5,9 @@
 //                 and pitches), plain ROW/COL layouts directly; blocked A and the
 //                 blocked / VNNI layouts of B through unpacks to row-major in the
 //                 caller's workspace
-//                 f32 operands of plain layouts as a six-term bf16 split over a 6x longer K
-//   FFMA          everything else (small or oddly pitched f32, f32 blocked layouts), exact f32
+//                 f32 operands (plain or 32x32-blocked, batched or not) as a six-term
+//                 bf16 split over a 6x longer K
+//   FFMA          everything else (small or oddly pitched f32, explicit f32 split-K), exact f32
 // The choice mirrors the dispatcher of helion_mlir_utils/matmul.py:1446-1570
 // (bf16 -> fused kernel, f32 -> split-K / fused / blocked) with the CPU tile
 // heuristics replaced by the SM count; block_sizes arrive as tile_m/n/k hints.
@@ -24,23 +25,25 @@ int run_wait_timeout_selftest(unsigned long long budget_ns, cudaStream_t stream)
 int run_gemm_simt(const b200_gemm_desc& d, const GemmOperand& a, const GemmOperand& b, const GemmEpilogue& epi,
                   int splits, float* workspace, cudaStream_t stream);
 
-int launch_split_f32(const float* src, void* dst, int64_t rows, int64_t cols, int64_t ld, bool is_b, bool along_cols,
-                     cudaStream_t stream);
-
 namespace {
 
 // f32 operands on the tensor cores: each f32 value is split into three bf16 parts
 // and the six largest cross products are summed by one bf16 GEMM over a six times
 // longer K (the bf16 analogue of 3xTF32; products of bf16 parts are exact in f32).
 // The tensor core's f32 accumulation truncates, a bias that grows with the length
-// and magnitude of a running sum (measured: relative Frobenius error 1.0e-6 at
-// K=1024, 4.4e-6 at K=4096 against the 1e-5 bar). So long sums are cut into chunks
-// of kSplitChunkK widened-K elements that the epilogue adds in f32 (serial split-K),
-// and K above kSplitMaxK stays on the exact FFMA kernel.
+// and magnitude of a running sum. So the widened K is cut into chunks of at most
+// kSplitChunkK elements that are added in f32 in ascending order (serial split-K, or
+// parallel partial sums when there are few tiles): the error then no longer grows with K
+// (measured relative Frobenius error 1.0e-6 at 1024^3, 4.4e-6 at 4096^3, bar 1e-5).
+// Operands that are not finite, or beyond bf16's range (|x| > 3.39e38), have no such
+// split: their products come out NaN where exact f32 arithmetic gives an infinity.
 constexpr int kSplitTerms = 6;
 constexpr int64_t kSplitChunkK = 2048;
-constexpr int64_t kSplitMaxK = 4096;
-constexpr int64_t kSplitMinWork = int64_t(1) << 24;  // m*n*k below this stays on the FFMA kernel
+constexpr int64_t kSplitMaxK = int64_t(1) << 17;
+constexpr int64_t kSplitMinWork = int64_t(1) << 24;  // batch*m*n*k below this stays on the FFMA kernel
+
+// K of one copy in the widened operands: whole 16-byte pieces of bf16.
+inline int64_t split_k_wide(const b200_gemm_desc& d) { return round_up(d.k, 8); }
 
 struct Resolved {
   GemmOperand a, b;
@@ -56,15 +59,14 @@ struct Resolved {
   size_t split_partial_bytes;  // ... and for its K chunks as parallel partial sums (0: chunks run back to back)
 };
 
-// Whether the f32 GEMM `d` can run as a widened bf16 GEMM (layouts TMA can describe).
 // K chunks of the widened product. At least one per kSplitChunkK elements; when the
 // chunks run as parallel work items (few output tiles), as many more as there are idle
 // CTA pairs for, so that each chunk is shorter (1024^3: 16 tiles x 4 chunks of 1536 on
 // 74 pairs instead of 3 of 2048). Shorter chunks only make the f32 sum more exact.
 int64_t split_chunk_count(const b200_gemm_desc& d, bool* parallel) {
-  const int64_t wide_k = d.k * kSplitTerms;
+  const int64_t wide_k = split_k_wide(d) * kSplitTerms;
   int64_t chunks = ceil_div(wide_k, kSplitChunkK);
-  const int64_t pair_tiles = ceil_div(d.m, 256) * ceil_div(d.n, 256);
+  const int64_t pair_tiles = ceil_div(d.m, 256) * ceil_div(d.n, 256) * d.batch;
   const int64_t pairs = device_info().sm_count / 2;
   *parallel = chunks > 1 && pair_tiles * chunks <= pairs;
   if (*parallel) {
@@ -79,14 +81,17 @@ int64_t split_chunk_count(const b200_gemm_desc& d, bool* parallel) {
   return chunks;
 }
 
+// Whether the f32 GEMM `d` can run as a widened bf16 GEMM: plain or 32x32-blocked
+// operands (the widening pass reads either), any batch, no explicit split-K (that
+// keeps the exact kernel and its partial sums).
 bool f32_split_applies(const b200_gemm_desc& d) {
-  if (d.dtype != B200_F32 || d.a_layout > B200_LAYOUT_COL || d.b_layout > B200_LAYOUT_COL) return false;
-  if (d.batch != 1 || d.split_k > 1 || d.k < 1 || d.k > kSplitMaxK) return false;
-  if (d.m * d.n * d.k < kSplitMinWork) return false;
-  // row pitches of the widened operands must be multiples of 16 bytes
-  const bool a_ok = d.a_layout == B200_LAYOUT_ROW ? d.k % 4 == 0 : d.m % 8 == 0;
-  const bool b_ok = d.b_layout == B200_LAYOUT_COL ? d.k % 4 == 0 : d.n % 8 == 0;
-  return a_ok && b_ok && d.k * kSplitTerms < (int64_t(1) << 30);
+  if (d.dtype != B200_F32 || d.a_layout > B200_LAYOUT_BLOCKED || d.b_layout > B200_LAYOUT_BLOCKED) return false;
+  if (d.split_k > 1 || d.k < 1 || d.k > kSplitMaxK || d.force_kernel == 2) return false;
+  if (static_cast<double>(d.batch) * d.m * d.n * d.k < static_cast<double>(kSplitMinWork)) return false;
+  // [K, M] / [K, N] operands are widened along their rows: the row pitch stays m / n elements
+  if (d.a_layout == B200_LAYOUT_COL && d.m % 8) return false;
+  if (d.b_layout == B200_LAYOUT_ROW && d.n % 8) return false;
+  return true;
 }
 
 int validate(const b200_gemm_desc* d, Resolved* r) {
@@ -164,14 +169,15 @@ int validate(const b200_gemm_desc* d, Resolved* r) {
       d->split_k > 1 ? static_cast<size_t>(d->split_k) * d->batch * d->m * d->n * sizeof(float) : 0;
   r->split_a_bytes = r->split_b_bytes = r->split_partial_bytes = 0;
   if (f32_split_applies(*d)) {
-    r->split_a_bytes = static_cast<size_t>(round_up(d->m * d->k * kSplitTerms * 2, 256));
-    r->split_b_bytes = static_cast<size_t>(round_up(d->n * d->k * kSplitTerms * 2, 256));
+    const int64_t kw = split_k_wide(*d);
+    r->split_a_bytes = static_cast<size_t>(round_up(d->batch * d->m * kw * kSplitTerms * 2, 256));
+    r->split_b_bytes = static_cast<size_t>(round_up(d->batch * d->n * kw * kSplitTerms * 2, 256));
     // Few output tiles: the K chunks of the widened product (added in f32 either way, in
     // the same order) run as parallel work items into partial sums, so that the chunks of
     // one tile occupy several SMs instead of running back to back on one.
     bool parallel = false;
     const int64_t chunks = split_chunk_count(*d, &parallel);
-    if (parallel) r->split_partial_bytes = static_cast<size_t>(round_up(chunks * d->m * d->n * 4, 256));
+    if (parallel) r->split_partial_bytes = static_cast<size_t>(round_up(chunks * d->batch * d->m * d->n * 4, 256));
   }
   return 0;
 }
@@ -197,15 +203,21 @@ b200_gemm_desc unpacked_desc(const b200_gemm_desc& d, const Resolved& r, void* a
 
 enum Path { kPathUmma, kPathUmmaUnpack, kPathUmmaSplitF32, kPathSimt };
 
-// The bf16 GEMM over the widened K that stands for the f32 GEMM `d`.
+// The bf16 GEMM over the widened K that stands for the f32 GEMM `d`: A as [M, 6K]
+// (or [6K, M] for a [K, M] source), B as [N, 6K] (or [6K, N] for a [K, N] source).
 b200_gemm_desc split_desc(const b200_gemm_desc& d, void* a_wide, void* b_wide) {
   b200_gemm_desc u = d;
+  const int64_t kw = split_k_wide(d);
   u.dtype = B200_BF16;
   u.a = a_wide;
   u.b = b_wide;
-  u.k = d.k * kSplitTerms;
-  u.lda = d.a_layout == B200_LAYOUT_ROW ? u.k : d.m;  // [M, 6K] or [6K, M]
-  u.ldb = d.b_layout == B200_LAYOUT_COL ? u.k : d.n;  // [N, 6K] or [6K, N]
+  u.k = kw * kSplitTerms;
+  u.a_layout = d.a_layout == B200_LAYOUT_COL ? B200_LAYOUT_COL : B200_LAYOUT_ROW;
+  u.b_layout = d.b_layout == B200_LAYOUT_ROW ? B200_LAYOUT_ROW : B200_LAYOUT_COL;
+  u.lda = u.a_layout == B200_LAYOUT_ROW ? u.k : d.m;
+  u.ldb = u.b_layout == B200_LAYOUT_COL ? u.k : d.n;
+  u.stride_a = d.m * u.k;
+  u.stride_b = d.n * u.k;
   // chunks of the widened K are added in f32 by the epilogue (needs an f32 result)
   bool parallel = false;
   u.split_k = static_cast<int32_t>(split_chunk_count(d, &parallel));
@@ -213,6 +225,29 @@ b200_gemm_desc split_desc(const b200_gemm_desc& d, void* a_wide, void* b_wide) {
   u.workspace = nullptr;
   u.workspace_bytes = 0;
   return u;
+}
+
+// The two operands of `d` as the widening pass reads them.
+void split_operands(const b200_gemm_desc& d, void* a_wide, void* b_wide, SplitOperand* a, SplitOperand* b) {
+  const int64_t kw = split_k_wide(d), kblocks = round_up(d.k, 32) / 32;
+  *a = SplitOperand{static_cast<const float*>(d.a), static_cast<__nv_bfloat16*>(a_wide), d.batch, 0, 0, 0, d.stride_a, kw,
+                    0, 0, 1};
+  if (d.a_layout == B200_LAYOUT_COL) {  // [K, M]: widened along the rows
+    a->rows = d.k, a->cols = d.m, a->ld = d.lda, a->along_cols = 0;
+  } else {
+    a->rows = d.m, a->cols = d.k;
+    a->ld = d.a_layout == B200_LAYOUT_ROW ? d.lda : kblocks;
+    a->layout = d.a_layout == B200_LAYOUT_ROW ? 0 : 1;
+  }
+  *b = SplitOperand{static_cast<const float*>(d.b), static_cast<__nv_bfloat16*>(b_wide), d.batch, 0, 0, 0, d.stride_b, kw,
+                    0, 1, 1};
+  if (d.b_layout == B200_LAYOUT_ROW) {  // [K, N]: widened along the rows
+    b->rows = d.k, b->cols = d.n, b->ld = d.ldb, b->along_cols = 0;
+  } else {
+    b->rows = d.n, b->cols = d.k;
+    b->ld = d.b_layout == B200_LAYOUT_COL ? d.ldb : kblocks;
+    b->layout = d.b_layout == B200_LAYOUT_COL ? 0 : 2;
+  }
 }
 
 // Chooses the path; `*why` gets the refusal of the tensor-core path when it is not taken.
@@ -288,12 +323,9 @@ extern "C" int b200_gemm(const b200_gemm_desc* desc, void* stream) {
 
   if (path == kPathUmmaSplitF32) {
     uint8_t* wide = static_cast<uint8_t*>(d.workspace);
-    const bool a_cols = d.a_layout == B200_LAYOUT_ROW, b_cols = d.b_layout == B200_LAYOUT_COL;
-    int rc = launch_split_f32(static_cast<const float*>(d.a), wide, a_cols ? d.m : d.k, a_cols ? d.k : d.m, d.lda,
-                              false, a_cols, s);
-    if (rc == 0)
-      rc = launch_split_f32(static_cast<const float*>(d.b), wide + r.split_a_bytes, b_cols ? d.n : d.k,
-                            b_cols ? d.k : d.n, d.ldb, true, b_cols, s);
+    SplitOperand wide_a, wide_b;
+    split_operands(d, wide, wide + r.split_a_bytes, &wide_a, &wide_b);
+    const int rc = launch_split_f32(wide_a, wide_b, s);
     if (rc != 0) return finish(rc);
     float* chunk_partials = nullptr;
     if (r.split_partial_bytes && d.workspace_bytes >= r.split_a_bytes + r.split_b_bytes + r.split_partial_bytes)

@@ -65,6 +65,18 @@ __device__ __forceinline__ int64_t offset_b(const GemmOperand& b, int64_t k, int
   }
 }
 
+// One f32 operand to be widened into its six-fold bf16 split (split_f32_kernel, pack.cu).
+struct SplitOperand {
+  const float* src;
+  __nv_bfloat16* dst;
+  int64_t batch, rows, cols;  // extent of the logical matrix read from the source
+  int64_t ld, batch_stride;   // source, in elements; blocked sources: ld = 32-blocks per block row
+  int64_t k_wide;             // contraction length of one copy in the widened operand (zero beyond the source's)
+  int32_t layout;             // 0 rows of `ld`; 1 blocks [rows/32][cols/32][32 r][32 c]; 2 blocks [rows/32][cols/32][32 c][32 r]
+  int32_t is_b, along_cols;
+};
+int launch_split_f32(const SplitOperand& a, const SplitOperand& b, cudaStream_t stream);
+
 // out = act((sum_s partial[s] + bias) * scale + shift), s ascending.
 // partial is [splits][batch*m*n] f32 (rows contiguous, n wide); out rows are ldc wide.
 int launch_splitk_reduce(const float* partial, int splits, int64_t batch, int64_t m, int64_t n, void* out,

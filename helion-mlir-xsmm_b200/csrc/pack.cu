@@ -8,7 +8,7 @@
 // `W` consecutive destination elements (16 bytes where the layout keeps that many
 // source elements adjacent); the VNNI unpacks are tiled transposes of 32-bit K
 // pairs through shared memory, 128-byte segments on both sides.
-#include "common.cuh"
+#include "gemm_common.cuh"
 
 namespace b200 {
 namespace {
@@ -351,30 +351,53 @@ __global__ void __launch_bounds__(256) unpack_b_blocked_kernel(const T* __restri
 //   A operand parts (3,2,1,2,1,1), B operand parts (1,2,3,1,2,1)
 //   -> a3 b1 + a2 b2 + a1 b3 + a2 b1 + a1 b2 + a1 b1, smallest terms first so that
 //      they are not absorbed by a large running sum.
-// along_cols: the contraction dimension is the column dimension (copies side by
-// side in a row, out [rows, 6*cols]); else the row dimension (out [6*rows, cols]).
-__global__ void __launch_bounds__(256) split_f32_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst,
-                                                        int64_t rows, int64_t cols, int64_t ld, int is_b,
-                                                        int along_cols) {
-  const int64_t total = rows * cols;
+// A value that is not finite, or that rounds to infinity in bf16, has no such split
+// (x - bf16(x) is NaN): its products come out NaN where exact f32 gives an infinity.
+//
+// One launch widens both operands of a GEMM. along_cols: the contraction dimension is
+// the column dimension of the logical matrix (copies side by side in a row, out
+// [batch][rows][6 * k_wide]); else the row dimension (out [batch][6 * k_wide][cols]).
+// k_wide >= the source's K: the rest of every copy is zero.
+__device__ __forceinline__ void split_one(const SplitOperand& o, int64_t i) {
+  const int64_t lead = o.along_cols ? o.rows : o.k_wide, inner = o.along_cols ? o.k_wide : o.cols;
+  const int64_t per_batch = lead * inner;
+  const int64_t bi = i / per_batch, rem = i - bi * per_batch;
+  const int64_t r = rem / inner, c = rem - r * inner;
+  float x = 0.f;
+  if (r < o.rows && c < o.cols) {
+    const float* src = o.src + bi * o.batch_stride;
+    if (o.layout == 0)
+      x = src[r * o.ld + c];
+    else if (o.layout == 1)
+      x = src[(((r >> 5) * o.ld + (c >> 5)) << 10) + ((r & 31) << 5) + (c & 31)];
+    else
+      x = src[(((r >> 5) * o.ld + (c >> 5)) << 10) + ((c & 31) << 5) + (r & 31)];
+  }
+  __nv_bfloat16 part[3];
+  part[0] = __float2bfloat16_rn(x);
+  const float r1 = x - __bfloat162float(part[0]);
+  part[1] = __float2bfloat16_rn(r1);
+  part[2] = __float2bfloat16_rn(r1 - __bfloat162float(part[1]));
+  const int pattern_a[6] = {2, 1, 0, 1, 0, 0}, pattern_b[6] = {0, 1, 2, 0, 1, 0};
+  __nv_bfloat16* dst = o.dst + bi * 6 * per_batch;
+#pragma unroll
+  for (int t = 0; t < 6; ++t) {
+    const __nv_bfloat16 v = part[o.is_b ? pattern_b[t] : pattern_a[t]];
+    if (o.along_cols)
+      dst[r * (6 * inner) + t * inner + c] = v;
+    else
+      dst[(t * lead + r) * inner + c] = v;
+  }
+}
+
+__global__ void __launch_bounds__(256) split_f32_kernel(const SplitOperand a, const SplitOperand b, int64_t total_a,
+                                                        int64_t total) {
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-    const int64_t r = i / cols, c = i - r * cols;
-    const float x = src[r * ld + c];
-    __nv_bfloat16 part[3];
-    part[0] = __float2bfloat16_rn(x);
-    const float r1 = x - __bfloat162float(part[0]);
-    part[1] = __float2bfloat16_rn(r1);
-    part[2] = __float2bfloat16_rn(r1 - __bfloat162float(part[1]));
-    const int pattern_a[6] = {2, 1, 0, 1, 0, 0}, pattern_b[6] = {0, 1, 2, 0, 1, 0};
-#pragma unroll
-    for (int t = 0; t < 6; ++t) {
-      const __nv_bfloat16 v = part[is_b ? pattern_b[t] : pattern_a[t]];
-      if (along_cols)
-        dst[r * (6 * cols) + t * cols + c] = v;
-      else
-        dst[(t * rows + r) * cols + c] = v;
-    }
+    if (i < total_a)
+      split_one(a, i);
+    else
+      split_one(b, i - total_a);
   }
 }
 
@@ -445,13 +468,15 @@ int run_pack(int kind, const PackParams& p, cudaStream_t stream) {
 
 }  // namespace
 
-// Widens an f32 GEMM operand into its six-fold bf16 split (see split_f32_kernel).
-int launch_split_f32(const float* src, void* dst, int64_t rows, int64_t cols, int64_t ld, bool is_b, bool along_cols,
-                     cudaStream_t stream) {
-  const int64_t wanted = ceil_div(rows * cols, 256), resident = static_cast<int64_t>(device_info().sm_count) * 16;
+// Widens both f32 operands of a GEMM into their six-fold bf16 splits (see split_f32_kernel).
+int launch_split_f32(const SplitOperand& a, const SplitOperand& b, cudaStream_t stream) {
+  auto count = [](const SplitOperand& o) {
+    return o.batch * (o.along_cols ? o.rows * o.k_wide : o.k_wide * o.cols);
+  };
+  const int64_t total_a = count(a), total = total_a + count(b);
+  const int64_t wanted = ceil_div(total, 256), resident = static_cast<int64_t>(device_info().sm_count) * 16;
   const unsigned grid = static_cast<unsigned>(wanted < resident ? (wanted > 0 ? wanted : 1) : resident);
-  split_f32_kernel<<<grid, 256, 0, stream>>>(src, static_cast<__nv_bfloat16*>(dst), rows, cols, ld, is_b ? 1 : 0,
-                                             along_cols ? 1 : 0);
+  split_f32_kernel<<<grid, 256, 0, stream>>>(a, b, total_a, total);
   return check_launch();
 }
 

@@ -11,6 +11,7 @@
 // it was last used on and an event recorded there; a request on the same stream
 // may take it at once (stream order protects it), a request on another stream
 // only when the event has completed.
+#include <atomic>
 #include <list>
 #include <mutex>
 #include <unordered_map>
@@ -66,6 +67,19 @@ void evict_over_limit(Pool& p) {
   }
 }
 
+// Host-side failure injection for tests of the retry below: the next `count` device
+// allocations of the pool fail with cudaErrorMemoryAllocation without reaching the
+// driver (no device is driven out of memory to test this).
+std::atomic<int> g_fail_allocations{0};
+
+cudaError_t pool_malloc(void** ptr, size_t bytes) {
+  int left = g_fail_allocations.load(std::memory_order_relaxed);
+  while (left > 0) {
+    if (g_fail_allocations.compare_exchange_weak(left, left - 1)) return cudaErrorMemoryAllocation;
+  }
+  return cudaMalloc(ptr, bytes);
+}
+
 void release_all(Pool& p) {
   for (Block& b : p.free_blocks) destroy(b);
   p.free_blocks.clear();
@@ -113,14 +127,14 @@ extern "C" int b200_pool_alloc(size_t bytes, void* stream, void** out_ptr, int32
   Block b;
   b.bytes = rounded;
   b.device = device;
-  err = cudaMalloc(&b.ptr, rounded);
+  err = pool_malloc(&b.ptr, rounded);
   if (err != cudaSuccess) {
     cudaGetLastError();
     {
       std::lock_guard<std::mutex> lock(p.mutex);
       release_all(p);
     }
-    err = cudaMalloc(&b.ptr, rounded);
+    err = pool_malloc(&b.ptr, rounded);
     if (err != cudaSuccess) {
       cudaGetLastError();
       return -static_cast<int>(err);
@@ -198,5 +212,11 @@ extern "C" int b200_pool_stats(b200_pool_stats_t* out) {
   out->max_bytes = p.max_bytes;
   out->live_blocks = p.live.size();
   out->live_bytes = p.live_bytes;
+  return 0;
+}
+
+extern "C" int b200_pool_inject_alloc_failures(int32_t count) {
+  if (count < 0) return B200_E_ARG;
+  g_fail_allocations.store(count, std::memory_order_relaxed);
   return 0;
 }

@@ -415,6 +415,13 @@ extern "C" int b200_column_sum(int32_t dtype, const void* x, float* out, int64_t
   return column_sum_impl(dtype, x, out, m, n, ld, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
+// The size check of b200_column_sum_static, against a given capacity: 0 when the
+// partial sums of an m x n column sum fit `capacity` bytes, else B200_E_TOO_LARGE.
+// Pure host arithmetic (no device needed).
+extern "C" int b200_column_sum_static_fits(int64_t m, int64_t n, size_t capacity) {
+  return column_sum_workspace(m, n) > capacity ? B200_E_TOO_LARGE : 0;
+}
+
 // Same result as b200_column_sum, for callers that must not allocate and have no
 // scratch of their own to lend: the partial sums go to the library's fixed array.
 extern "C" int b200_column_sum_static(int32_t dtype, const void* x, float* out, int64_t m, int64_t n, int64_t ld,
@@ -427,7 +434,7 @@ extern "C" int b200_column_sum_static(int32_t dtype, const void* x, float* out, 
   if (ld < n) return refuse(B200_E_STRIDE);
   if (device_info().sm_count == 0) return refuse(B200_E_DEVICE);
   // The partial sums of this shape must fit the fixed array.
-  if (column_sum_workspace(m, n) > kStaticScratchBytes) return refuse(B200_E_TOO_LARGE);
+  if (b200_column_sum_static_fits(m, n, kStaticScratchBytes) != 0) return refuse(B200_E_TOO_LARGE);
   void* scratch = nullptr;
   const int rc = static_scratch(&scratch);
   if (rc != 0) return finish(rc);

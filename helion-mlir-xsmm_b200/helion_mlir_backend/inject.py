@@ -18,6 +18,7 @@ from __future__ import annotations
 
 import logging
 from typing import Callable
+from typing import Sequence
 
 from .driver import CONFIG_KEYS
 from .driver import warn_misspelt_config_keys
@@ -91,8 +92,84 @@ def make_backend_class(base: type) -> type:
         def classify_autotune_exception(self, err: BaseException) -> str | None:
             return "warn" if isinstance(err, UnsupportedOperationError) else None
 
+        def autotune(self, bound_kernel: object, args: Sequence[object], *, force: bool = True, **kwargs: object) -> object:
+            """A config's ``block_sizes`` are tile hints here, so there is no space of
+            generated kernels to search (cf. ``MLIRBackend.autotune``,
+            ``_compiler/mlir/backend.py:81-103``, which narrows Helion's search to what its
+            target compiles). What is measured instead is the launch choice of the
+            hand-written GEMM for the operands at hand (tile width, CTA pairs, K splits:
+            ``helion_mlir_utils.tuning``), stored per hardware name where later calls
+            find it; the config returned is the kernel's first given one, else Helion's
+            default for its spec."""
+            return autotune_choice(bound_kernel, args, force=force, fallback=getattr(super(), "autotune", None), **kwargs)
+
+        def get_do_bench(self) -> Callable[..., float]:
+            """Timing function for Helion's autotuner (``backend.py:105-108`` returns a host
+            timer): CUDA events on the current stream, milliseconds per call."""
+            return do_bench
+
+        def get_interleaved_bench(self) -> Callable[..., list[float]]:
+            return interleaved_bench
+
     B200Backend.__name__ = "MLIRBackend"
     return B200Backend
+
+
+def do_bench(fn: Callable[[], object], *_: object, warmup: int = 3, rep: int = 20, **__: object) -> float:
+    """Milliseconds per call of ``fn`` (CUDA events on the current stream, after a warm-up)."""
+    from helion_mlir_utils import tuning
+
+    return tuning.time_call(fn, iterations=max(1, int(rep)), warmup=max(0, int(warmup))) * 1e-3
+
+
+def interleaved_bench(fns: Sequence[Callable[[], object]], *_: object, repeat: int = 20, **__: object) -> list[float]:
+    """Milliseconds per call of each function, the functions taking turns so that clock
+    changes fall on all of them alike."""
+    import torch
+
+    fns = list(fns)
+    for fn in fns:
+        fn()
+    totals = [0.0] * len(fns)
+    for _ in range(max(1, int(repeat))):
+        for i, fn in enumerate(fns):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            fn()
+            stop.record()
+            stop.synchronize()
+            totals[i] += start.elapsed_time(stop)
+    return [t / max(1, int(repeat)) for t in totals]
+
+
+def autotune_choice(bound_kernel: object, args: Sequence[object], *, force: bool = True,
+                    fallback: Callable[..., object] | None = None, **kwargs: object) -> object:
+    """See ``B200Backend.autotune``. Two bf16 matrices among ``args`` whose inner sizes
+    agree are taken as the operands of a recognised GEMM body and tuned; anything else
+    leaves the table alone."""
+    kernel = getattr(bound_kernel, "kernel", None)
+    fn = getattr(kernel, "fn", None)
+    configs = list(getattr(kernel, "configs", None) or [])
+    if fn is not None and force:
+        try:
+            import torch
+
+            from helion_mlir_utils import tuning
+
+            mats = [t for t in args if isinstance(t, torch.Tensor) and t.dim() == 2 and t.is_cuda and t.dtype == torch.bfloat16]
+            if len(mats) >= 2 and mats[0].shape[1] == mats[1].shape[0] and recognise(fn, configs[0] if configs else None) is not None:
+                tuning.tune_matmul(mats[0], mats[1])
+        except (RuntimeError, ValueError, ImportError) as exc:
+            log.debug("autotune: launch choice not measured: %s", exc)
+    if configs:
+        return configs[0]
+    spec = getattr(bound_kernel, "config_spec", None)
+    default = getattr(spec, "default_config", None)
+    if callable(default):
+        return default()
+    if fallback is not None:
+        return fallback(bound_kernel, args, force=force, **kwargs)
+    raise UnsupportedOperationError("autotune: the kernel has no config and no config spec to take a default from")
 
 
 def compile_config(bound_kernel: object, config: object, *, allow_print: bool = True) -> Callable[..., object]:

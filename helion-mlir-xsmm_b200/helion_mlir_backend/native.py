@@ -164,12 +164,14 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "b200_column_sum_workspace_bytes": (c_size_t, [c_int64, c_int64]),
     "b200_column_sum": (c_int, [c_int32, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_size_t, c_void_p]),
     "b200_column_sum_static": (c_int, [c_int32, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
+    "b200_column_sum_static_fits": (c_int, [c_int64, c_int64, c_size_t]),
     "b200_eltwise": (c_int, [c_int32, c_int32, c_void_p, c_void_p, c_int64, c_float, c_void_p]),
     "b200_pool_alloc": (c_int, [c_size_t, c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_int32)]),
     "b200_pool_free": (c_int, [c_void_p, c_void_p]),
     "b200_pool_set_limit": (c_int, [c_size_t]),
     "b200_pool_release": (c_int, []),
     "b200_pool_stats": (c_int, [ctypes.POINTER(PoolStats)]),
+    "b200_pool_inject_alloc_failures": (c_int, [c_int32]),
     "b200_get_counters": (c_int, [ctypes.POINTER(Counters)]),
     "b200_reset_counters": (c_int, []),
     "b200_read_kernel_status": (c_int, [c_void_p, ctypes.POINTER(c_int32)]),

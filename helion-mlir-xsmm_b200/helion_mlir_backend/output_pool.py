@@ -64,11 +64,15 @@ _DTYPES = frozenset(
 class _Lease:
     """A block of the library's device pool on loan to one torch storage."""
 
-    __slots__ = ("__cuda_array_interface__", "device", "pointer")
+    __slots__ = ("__cuda_array_interface__", "device", "pointer", "stream")
 
-    def __init__(self, pointer: int, nbytes: int, device: torch.device) -> None:
+    def __init__(self, pointer: int, nbytes: int, device: torch.device, stream: int) -> None:
         self.pointer = pointer
         self.device = device
+        # The stream the block was allocated for, and on which every tensor shaped onto it
+        # is handed out (a block is only reused for requests on that stream): the library
+        # orders the block's next use after the work enqueued there.
+        self.stream = stream
         self.__cuda_array_interface__ = {
             "shape": (nbytes,),
             "typestr": "|u1",
@@ -78,12 +82,12 @@ class _Lease:
         }
 
     def __del__(self) -> None:
-        # Runs wherever the storage dies (any thread, the garbage collector,
-        # interpreter exit): never raises.
+        # Runs wherever the storage dies (any thread, any current stream, the garbage
+        # collector, interpreter exit): never raises, and names the block's own stream,
+        # not the one that happens to be current.
         try:
-            stream = torch.cuda.current_stream(self.device).cuda_stream
             with native.on_device(self.device):
-                native.module().b200_pool_free(self.pointer, stream)
+                native.module().b200_pool_free(self.pointer, self.stream)
         except Exception:  # noqa: BLE001
             pass
 
@@ -163,8 +167,8 @@ def _settle_locked() -> None:
         free = free[1:]
 
 
-def _wrap(pointer: int, rounded: int, device: torch.device) -> torch.UntypedStorage | None:
-    lease = _Lease(pointer, rounded, device)  # its __del__ returns the block, also on failure below
+def _wrap(pointer: int, rounded: int, device: torch.device, stream: int) -> torch.UntypedStorage | None:
+    lease = _Lease(pointer, rounded, device, stream)  # its __del__ returns the block, also on failure below
     try:
         flat = torch.as_tensor(lease, device=device)
         del lease  # the storage now owns the only reference
@@ -211,7 +215,7 @@ def _allocate(sizes: tuple[int, ...], count: int, dtype: torch.dtype, device: to
             code = lib.b200_pool_alloc(nbytes, stream, ctypes.byref(pointer), ctypes.byref(hit))
         if code != 0 or not pointer.value:
             return None  # torch's own attempt raises its error
-        storage = _wrap(pointer.value, rounded, device)
+        storage = _wrap(pointer.value, rounded, device, stream)
         if storage is None:
             return None
         # Shaped in place on the pool's storage: a plain tensor, not a view.

@@ -115,3 +115,21 @@ __all__ = [
     "vnni_panel",
     "whole_row_tiles",
 ]
+
+# HELION_MLIR_TRACE_CALLS=1: every operator reports the first call with each kind of
+# operands and an at-exit summary counts the calls. Unset: nothing is wrapped.
+_OPERATORS = [
+    "attention", "bmm", "column_sum", "group_norm", "layer_norm", "leaky_relu", "linear", "linear_affine", "matmul",
+    "matmul_blocked", "matmul_host", "matmul_prepacked_b", "matmul_prepacked_b_affine", "matvec", "pack_a_blocked",
+    "pack_a_blocked_t", "pack_b_blocked", "pack_b_blocked_t", "pack_b_blocked_vnni", "pack_b_blocked_vnni_t",
+    "pack_b_vnni_t", "pad_2d", "relu", "rms_norm", "row_dot", "row_sum", "scalar_mul", "softmax", "stream_rows",
+]
+
+
+def _install_tracing() -> None:
+    from helion_mlir_backend import call_trace
+
+    call_trace.install(globals(), _OPERATORS)
+
+
+_install_tracing()

@@ -24,6 +24,7 @@ from __future__ import annotations
 
 from collections import OrderedDict
 import ctypes
+import threading
 from typing import TYPE_CHECKING
 from typing import Callable
 
@@ -218,6 +219,9 @@ def whole_row_tiles(m: int, n: int, panel: int | None = None) -> tuple[int, int]
     return None
 
 
+_F32_TENSOR_CORE_MIN_WORK = 1 << 24  # m*n*k from which f32 GEMMs run as widened bf16 products (gemm.cu)
+
+
 def _split_k(m: int, n: int, k: int, batch: int = 1) -> int:
     """Parallel K splits of a GEMM with fewer output tiles than SMs (0: none): the
     largest power of two that still leaves every SM at most one work item and
@@ -283,8 +287,8 @@ class GemmPlan:
         d = desc
         # packed bf16 operands are unpacked into scratch for the tensor cores
         packed = d.dtype == native.BF16 and (d.a_layout == native.LAYOUT_BLOCKED or d.b_layout >= native.LAYOUT_BLOCKED)
-        # f32 operands of plain layouts run as a widened bf16 GEMM built in scratch
-        widened = d.dtype == native.F32 and d.a_layout <= native.LAYOUT_COL and d.b_layout <= native.LAYOUT_COL
+        # f32 operands (plain or 32x32-blocked) run as a widened bf16 GEMM built in scratch
+        widened = d.dtype == native.F32 and d.a_layout <= native.LAYOUT_BLOCKED and d.b_layout <= native.LAYOUT_BLOCKED
         self._wants_workspace = packed or widened or (d.split_k > 1 and parallel_split)
         self._workspace_need: int | None = None
 
@@ -302,16 +306,24 @@ class GemmPlan:
         lib = native.module()
         workspace = None
         desc.workspace, desc.workspace_bytes = None, 0
+        fresh_need = False
         if self._wants_workspace:
             need = self._workspace_need
-            if need is None:  # a function of the planned sizes and layouts only
-                need = self._workspace_need = int(lib.b200_gemm_workspace_bytes(ctypes.byref(desc)))
+            if need is None:
+                # A function of the planned sizes and layouts (and of the device's SM count),
+                # but the query also validates this call's pointers and answers 0 for a call
+                # it refuses: the figure is only kept once the call it came with has run.
+                fresh_need = True
+                with native.on_device(self.device):
+                    need = int(lib.b200_gemm_workspace_bytes(ctypes.byref(desc)))
             if need:
                 workspace = output_pool.empty((need,), dtype=torch.uint8, device=self.device)
                 desc.workspace, desc.workspace_bytes = workspace.data_ptr(), need
         with native.on_device(self.device):
             code = lib.b200_gemm(ctypes.byref(desc), native.stream_ptr(self.device))
         native.check("b200_gemm", code)
+        if fresh_need:
+            self._workspace_need = need
         self.launches += 1
         if self.post is not None:
             out = self.post(out).to(self.final_dtype)
@@ -428,14 +440,23 @@ _PLANS: OrderedDict[tuple[object, ...], GemmPlan] = OrderedDict()
 _PLANS_SIZE = 64
 
 
+_PLANS_LOCK = threading.Lock()
+
+
 def _cached_plan(key: tuple[object, ...], build: Callable[[], GemmPlan]) -> GemmPlan:
-    plan = _PLANS.get(key)
-    if plan is None:
-        plan = _PLANS[key] = build()
-        if len(_PLANS) > _PLANS_SIZE:
-            _PLANS.popitem(last=False)
-    else:
+    """Plans are shared between threads: the table is only touched under its lock
+    (building a plan, which may consult the tuning table, happens outside it)."""
+    with _PLANS_LOCK:
+        plan = _PLANS.get(key)
+        if plan is not None:
+            _PLANS.move_to_end(key)
+            return plan
+    built = build()
+    with _PLANS_LOCK:
+        plan = _PLANS.setdefault(key, built)
         _PLANS.move_to_end(key)
+        while len(_PLANS) > _PLANS_SIZE:
+            _PLANS.popitem(last=False)
     return plan
 
 
@@ -484,7 +505,11 @@ def _matmul_plan(
             if picked.split_k > 1 and plain and splits is None:
                 splits = picked.split_k
         if splits is None:
-            splits = _split_k(m, n, k) if plain else 0
+            # f32 problems large enough for the tensor cores (the widened product) spread their
+            # K chunks over idle SMs themselves; a split chosen here would keep them on the
+            # exact FFMA kernel, which only an explicit split_k asks for.
+            widened = a.dtype == torch.float32 and m * n * k >= _F32_TENSOR_CORE_MIN_WORK
+            splits = _split_k(m, n, k) if plain and not widened else 0
         return _plan_gemm(
             a=a, m=m, n=n, k=k,
             a_layout=native.LAYOUT_COL if trans_a else native.LAYOUT_ROW,
@@ -508,7 +533,8 @@ def tune_key(dtype: torch.dtype, m: int, n: int, k: int, trans_a: bool, trans_b:
 
 def forget_plans() -> None:
     """Drops the cached launch plans (after the tuning table changed)."""
-    _PLANS.clear()
+    with _PLANS_LOCK:
+        _PLANS.clear()
 
 
 def matmul(
@@ -536,6 +562,12 @@ def matmul(
     accumulator to another type than ``a.dtype``; ``split_k`` forces that many K
     splits, added in ascending order (default: chosen from the SM count for
     plain GEMMs with few output tiles).
+
+    f32 operands with ``m * n * k >= 2**24`` run on the tensor cores as six bf16
+    cross products per f32 product (relative Frobenius error about 1e-6, bar 1e-5);
+    that path has no representation for values that are not finite or exceed
+    bf16's range (|x| > 3.39e38), whose products come out NaN where exact f32
+    arithmetic gives an infinity. An explicit ``split_k`` keeps the exact f32 kernel.
 
     Raises ``ValueError`` if the operands aren't compatible (see
     :func:`supports`) instead of silently falling back to eager PyTorch.
@@ -956,12 +988,8 @@ def matmul_blocked(
 # --------------------------------------------------------------------------- batched
 
 
-def bmm(a: Tensor, b: Tensor, split_k: int | None = None, out_dtype: torch.dtype | None = None) -> Tensor:
-    """Batched ``A @ B`` of ``[B, M, K]`` and ``[B, K, N]`` with the batch as a grid
-    dimension of one kernel (bf16: tensor cores, operands read in place; f32:
-    FFMA). ``split_k`` (an extension): that many K splits per output tile, each
-    accumulated from zero in f32 and added in ascending order. ``out_dtype`` (an
-    extension): the type the f32 result is rounded to (default ``a.dtype``)."""
+def _bmm_plan(a: Tensor, b: Tensor, split_k: int | None, out_dtype: torch.dtype | None) -> tuple[GemmPlan, Tensor, Tensor]:
+    """Validates the operands of :func:`bmm` and plans the call."""
     if a.dim() != 3:
         raise ValueError(f"bmm() expects 3-D operands, got {tuple(a.shape)}")
     batch, m, k = map(int, a.shape)
@@ -989,4 +1017,25 @@ def bmm(a: Tensor, b: Tensor, split_k: int | None = None, out_dtype: torch.dtype
             strides=(m * k, k * n, m * n), split_k=splits, parallel_split=parallel, out_shape=(batch, m, n),
         )
 
-    return _cached_plan(key, build).run(a, b)
+    return _cached_plan(key, build), a, b
+
+
+def bmm(a: Tensor, b: Tensor, split_k: int | None = None, out_dtype: torch.dtype | None = None) -> Tensor:
+    """Batched ``A @ B`` of ``[B, M, K]`` and ``[B, K, N]`` with the batch as a grid
+    dimension of one kernel (bf16: tensor cores, operands read in place; f32:
+    the widened bf16 product from ``batch * m * n * k >= 2**24``, the exact FFMA kernel below that
+    and with ``split_k``). ``split_k`` (an extension): that many K splits per output tile, each
+    accumulated from zero in f32 and added in ascending order. ``out_dtype`` (an
+    extension): the type the f32 result is rounded to (default ``a.dtype``)."""
+    plan, a, b = _bmm_plan(a, b, split_k, out_dtype)
+    trace(f"bmm {tuple(a.shape)} x {tuple(b.shape)}")
+    return plan.run(a, b)
+
+
+def explain_bmm(a: Tensor, b: Tensor, split_k: int | None = None, out_dtype: torch.dtype | None = None) -> CallExplanation:
+    """What :func:`bmm` would launch for these operands."""
+    plan, a, b = _bmm_plan(a, b, split_k, out_dtype)
+    return plan.explain(a, b)
+
+
+bmm.explain = explain_bmm  # type: ignore[attr-defined]

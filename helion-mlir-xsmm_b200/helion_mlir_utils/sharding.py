@@ -82,4 +82,17 @@ def column_sharded_linear(
             return matmul(a, w, trans_b=True, bias=bias, epilogue=epilogue or identity_epilogue)
 
     local = op(x, weight_shard, bias_shard)
-    return gather_rows(local, out_features, group=group, dim=1)
+    return gather_columns(local, out_features, group=group)
+
+
+def gather_columns(local: Tensor, total: int, group: dist.ProcessGroup | None = None) -> Tensor:
+    """The ranks' column shards ``[M, N_r]`` put together as ``[M, N]`` on every rank. Equal
+    shards on CUDA devices take one NCCL all-gather into ``[G, M, N/G]`` and one strided copy;
+    anything else goes through :func:`gather_rows`."""
+    world = dist.get_world_size(group)
+    if local.is_cuda and local.dim() == 2 and total % world == 0 and local.shape[1] == total // world:
+        local = local.contiguous()
+        stacked = torch.empty((world, *local.shape), dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(stacked, local, group=group)
+        return stacked.permute(1, 0, 2).reshape(local.shape[0], total)
+    return gather_rows(local, total, group=group, dim=1)

@@ -259,6 +259,11 @@ int b200_column_sum(int32_t dtype, const void* x, float* out, int64_t m, int64_t
 #define B200_COLUMN_SUM_STATIC_MAX_BYTES (2u << 20)
 int b200_column_sum_static(int32_t dtype, const void* x, float* out, int64_t m, int64_t n, int64_t ld,
                            void* stream);
+/* The size check b200_column_sum_static applies, against any capacity: 0 when the
+ * partial sums of an m x n column sum fit `capacity` bytes, B200_E_TOO_LARGE when
+ * they do not (the entry point passes B200_COLUMN_SUM_STATIC_MAX_BYTES). Host
+ * arithmetic only: callable without a device. No counterpart in the reference. */
+int b200_column_sum_static_fits(int64_t m, int64_t n, size_t capacity);
 
 /* Elementwise y = f(x) over `count` contiguous elements; y may equal x.
  * Replaces _relu_kernel, _leaky_relu_kernel, _scalar_mul_kernel (elementwise.py:14-41). */
@@ -282,6 +287,12 @@ typedef struct b200_pool_stats_t {
   uint64_t hits, misses, free_blocks, free_bytes, max_bytes, live_blocks, live_bytes;
 } b200_pool_stats_t;
 int b200_pool_stats(b200_pool_stats_t* out);
+/* Test hook: the pool's next `count` device allocations fail (as if out of memory)
+ * without reaching the driver, so that the release-and-retry of b200_pool_alloc
+ * can be exercised on the host. The reference provokes the same path by capping
+ * the address space (tests/test_output_pool.py:683-709); a device is not driven
+ * out of memory for a test. 0 clears it. */
+int b200_pool_inject_alloc_failures(int32_t count);
 
 /* Per-operator counters since load: launches and refusals (cf. KernelRun's
  * native_calls / refusals, call.cpp:841-850). */

@@ -78,3 +78,22 @@ def test_refusals_are_codes_not_crashes() -> None:
         assert lib.b200_softmax(native.F32, None, None, 4, 4, 4, None) == native.E_DISABLED
     finally:
         native.set_native_call(True)
+
+
+def test_static_scratch_size_check_refuses_beyond_the_capacity() -> None:
+    """The check that keeps b200_column_sum_static inside its fixed array, called with
+    capacities other than the array's: under the present launch plan no shape needs more than
+    the 2 MiB the array has, so the refusal only shows against a smaller capacity."""
+    lib = native.module()
+    too_large = 11
+    assert "capacity" in native.strerror(too_large)
+    limit = 2 << 20
+    shapes = [(m, n) for m in (1, 64, 4096, 37888, 1 << 20, 1 << 24) for n in (1, 96, 443, 512, 1024, 4096, 65536, 1 << 20)]
+    for m, n in shapes:
+        need = int(lib.b200_column_sum_workspace_bytes(m, n))
+        assert need <= limit
+        assert lib.b200_column_sum_static_fits(m, n, limit) == 0
+        if need > 0:
+            assert lib.b200_column_sum_static_fits(m, n, need) == 0  # exactly fits
+            assert lib.b200_column_sum_static_fits(m, n, need - 1) == too_large
+    assert max(int(lib.b200_column_sum_workspace_bytes(m, n)) for m, n in shapes) == limit  # the bound is met, not just respected

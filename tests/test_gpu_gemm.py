@@ -293,3 +293,68 @@ def test_seeded_shape_sweep(ops) -> None:
         out = ops.matmul(da, db, trans_a=trans_a, trans_b=trans_b, bias=None if bias is None else cuda(bias), epilogue=fn)
         expect = ref.matmul(a, b, bias=bias, epilogue=fn)
         checks.assert_parity(BF16, out.cpu(), expect, f"case {case}: {(m, n, k)} ta={trans_a} tb={trans_b} {fn.__name__}")
+
+
+def _explains_tensor_cores(text: str) -> bool:
+    return "f32 as 6 bf16 cross products" in text and "umma_bf16" in text
+
+
+def test_f32_contractions_on_tensor_cores(ops) -> None:
+    """f32 GEMMs beyond the plain 2-D case run as the widened bf16 product: batched,
+    K above 4096 (more ordered chunks), 32x32-blocked operands and the prepacked-rows
+    layout. Relative Frobenius error against the f64 oracle <= 1e-5 (the bar of
+    tests/test_cpu_utils_f32_fused.py:58-140 is 1e-6 in max-norm for the exact kernel;
+    BASELINE's bar for f32 paths is 1e-5 Frobenius)."""
+    gen = torch.Generator().manual_seed(77)
+    # batched (bmm, _bmm_direct of the reference: matmul.py:1842-1855)
+    a, b = rand(gen, 8, 512, 1024, dtype=F32), rand(gen, 8, 1024, 384, dtype=F32)
+    da, db = cuda(a, b)
+    assert _explains_tensor_cores(str(ops.bmm.explain(da, db)))
+    assert checks.rel_frobenius(ops.bmm(da, db).cpu(), ref.bmm(a, b)) <= 1e-5
+    # K above 4096: twelve serial chunks per tile
+    a, b = rand(gen, 1024, 8192, dtype=F32), rand(gen, 8192, 768, dtype=F32)
+    da, db = cuda(a, b)
+    text = str(ops.matmul.explain(da, db))
+    assert _explains_tensor_cores(text) and "serial_splits=24" in text, text
+    assert checks.rel_frobenius(ops.matmul(da, db).cpu(), ref.matmul(a, b)) <= 1e-5
+    # few tiles and K >= 2048: no heuristic split-K keeps it off the tensor cores
+    a, b = rand(gen, 512, 4096, dtype=F32), rand(gen, 4096, 512, dtype=F32)
+    da, db = cuda(a, b)
+    assert _explains_tensor_cores(str(ops.matmul.explain(da, db)))
+    assert checks.rel_frobenius(ops.matmul(da, db).cpu(), ref.matmul(a, b)) <= 1e-5
+    # an explicit split_k keeps the exact kernel and its partial sums
+    assert "simt_ffma" in str(ops.matmul.explain(da, db, split_k=4))
+    # 32x32-blocked f32 operands (matmul.py:157-228) and the prepacked-rows layout (matmul.py:594-627)
+    m, n, k = 520, 300, 1000
+    a, b, bias = rand(gen, m, k, dtype=F32), rand(gen, k, n, dtype=F32), rand(gen, n, dtype=F32)
+    a4, b4 = ref.pack_a_blocked(a), ref.pack_b_blocked(b)
+    expect = ref.matmul(a, b, bias=bias, epilogue=torch.relu)
+    out = ops.matmul_blocked(*cuda(a4, b4), m, n, k, bias=cuda(bias), epilogue=torch.relu)
+    assert out.dtype == F32 and checks.rel_frobenius(out.cpu(), expect) <= 1e-5
+    rows = ops.matmul_prepacked_b(cuda(a), cuda(ref.pack_b_blocked_t(b.T.contiguous())), n, cuda(bias), torch.relu)
+    assert checks.rel_frobenius(rows.cpu(), expect) <= 1e-5
+    # all four orientations with ragged sizes (widening along rows for [K, M] / [K, N] operands)
+    m, n, k = 264, 520, 300
+    a, b = rand(gen, m, k, dtype=F32), rand(gen, k, n, dtype=F32)
+    for trans_a in (False, True):
+        for trans_b in (False, True):
+            a_in = a.T.contiguous() if trans_a else a
+            b_in = b.T.contiguous() if trans_b else b
+            out = ops.matmul(*cuda(a_in, b_in), trans_a=trans_a, trans_b=trans_b)
+            assert checks.rel_frobenius(out.cpu(), ref.matmul(a, b)) <= 1e-5, (trans_a, trans_b)
+
+
+@pytest.mark.parametrize("positive", [False, True], ids=["zero_mean", "positive_mean"])
+def test_f32_widened_product_long_sums(ops, positive: bool) -> None:
+    """The widened path at K = 4096 with enough tiles that the chunks run back to back on one
+    CTA, on N(0,1) operands and on uniform [0,1) operands (every partial sum of one sign,
+    which is where a truncating accumulator's bias adds up)."""
+    gen = torch.Generator().manual_seed(78 + positive)
+    make = (lambda *s: torch.rand(*s, generator=gen)) if positive else (lambda *s: torch.randn(*s, generator=gen))
+    a, b = make(1024, 4096), make(4096, 1024)
+    da, db = cuda(a, b)
+    text = str(ops.matmul.explain(da, db))
+    assert _explains_tensor_cores(text) and "parallel_splits=1" in text, text
+    assert checks.rel_frobenius(ops.matmul(da, db).cpu(), ref.matmul(a, b)) <= 1e-5
+    a3, b3 = make(1536, 2048), make(2048, 1536)
+    assert checks.rel_frobenius(ops.matmul(*cuda(a3, b3)).cpu(), ref.matmul(a3, b3)) <= 1e-5

@@ -195,3 +195,87 @@ def test_linear_cache_key_tracks_versions() -> None:
     p.data.mul_(2)
     assert _parameter_key(p) == k1  # .data changes are not (documented)
     assert ops.cache_prepacked_weights() is True
+
+
+def test_call_tracing_reports_first_calls_and_summarises(monkeypatch: pytest.MonkeyPatch, capsys: pytest.CaptureFixture[str]) -> None:
+    """HELION_MLIR_TRACE_CALLS: one line for the first call of an operator with each kind of
+    operands, a line for a call that raises, and per-operator counts in the at-exit summary
+    (the reference: _compiler/call_trace.py:220-386). Off, nothing is wrapped."""
+    from helion_mlir_backend import call_trace
+
+    def op(x, flag=False):
+        if flag:
+            raise ValueError("refused on purpose")
+        return x
+
+    op.explain = lambda *a, **k: call_trace.CallExplanation(True, "one kernel")
+    namespace = {"op": op, "LinearCache": dict}
+    monkeypatch.setattr(call_trace, "_trace", False)
+    call_trace.install(namespace, ["op", "LinearCache"])
+    assert namespace["op"] is op
+    monkeypatch.setattr(call_trace, "_trace", True)
+    monkeypatch.setattr(call_trace, "_summary_registered", True)  # no atexit hook from a test
+    call_trace.install(namespace, ["op", "LinearCache", "missing"])
+    traced = namespace["op"]
+    assert traced is not op and namespace["LinearCache"] is dict and traced.explain is op.explain
+    x32, x16 = torch.zeros(2, 3), torch.zeros(4, dtype=torch.bfloat16)
+    traced(x32), traced(x32), traced(x16)
+    with pytest.raises(ValueError):
+        traced(x32, flag=True)
+    err = capsys.readouterr().err.splitlines()
+    assert err == [
+        "[helion-mlir] op(float32[2d]): native, one kernel",
+        "[helion-mlir] op(bfloat16[1d]): native, one kernel",
+        "[helion-mlir] op(float32[2d]): raised ValueError: refused on purpose",
+    ]
+    lines = call_trace.summary_lines()
+    assert lines[0] == "at exit: op: 4 calls; raised: 1"
+    assert lines[-1].startswith("at exit: library")
+
+
+def test_environment_turns_the_pool_off_at_import(tmp_path) -> None:
+    """tests/test_output_pool.py:333-345: HELION_MLIR_OUTPUT_POOL=0 read at import."""
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    code = (
+        "import sys; sys.path.insert(0, r'%s'); "
+        "from helion_mlir_backend import output_pool as p; "
+        "print(p.output_pool_stats()['max_bytes'], p.enabled())" % (root / "helion-mlir-xsmm_b200")
+    )
+    import os
+
+    done = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300,
+                          env={**os.environ, "HELION_MLIR_OUTPUT_POOL": "0"})
+    assert done.returncode == 0, done.stderr
+    assert done.stdout.split() == ["0", "False"]
+
+
+def test_pool_falls_back_to_torch_for_what_it_does_not_take() -> None:
+    """tests/test_output_pool.py:463-489: other devices, bad sizes, quantized, strided,
+    conjugate and subclass tensors give exactly what torch's own functions give."""
+    from helion_mlir_backend import output_pool
+
+    before = output_pool.output_pool_stats()
+    big, f32, cpu = (256, 256), torch.float32, torch.device("cpu")
+    assert output_pool.empty((8, 8), dtype=f32, device=cpu).shape == (8, 8)
+    assert output_pool.empty(big, dtype=f32, device=torch.device("meta")).is_meta
+    with pytest.raises(RuntimeError):
+        output_pool.empty((-1, 256), dtype=f32, device=cpu)
+    with pytest.raises(TypeError):
+        output_pool.empty(("a", 256), dtype=f32, device=cpu)
+    assert output_pool.empty(big, dtype=torch.qint8, device=cpu).is_quantized
+    x = torch.randn(256, 256)
+    assert output_pool.empty_like(x[::2]).shape == (128, 256)
+    assert output_pool.empty_like(x.t()).shape == big
+    conjugate = torch.randn(256, 256, dtype=torch.complex64).conj()
+    assert output_pool.empty_like(conjugate).is_conj() == torch.empty_like(conjugate).is_conj()
+
+    class Sub(torch.Tensor):
+        pass
+
+    assert type(output_pool.empty_like(x.as_subclass(Sub))) is Sub
+    after = output_pool.output_pool_stats()
+    assert (after["hits"], after["misses"]) == (before["hits"], before["misses"])

@@ -77,6 +77,16 @@ def test_install_registers_and_routes(fake_helion) -> None:
     assert callable(native_op) and native_op != "helion-original"
     with pytest.raises(UnsupportedOperationError, match="matches none of them"):
         fake_helion.BoundKernel(something_else, backend).compile_config({"block_sizes": []})
+    # autotune / benchmarking hooks Helion calls on the backend (backend.py:81-113 of the reference)
+    ours.kernel.configs = [{"block_sizes": [128, 8]}, {"block_sizes": [64, 8]}]
+    assert backend.autotune(ours, (), force=True) == {"block_sizes": [128, 8]}  # hints only: the first config stands
+    ours.kernel.configs = []
+    ours.config_spec = types.SimpleNamespace(default_config=lambda: {"block_sizes": [1, 1]})
+    assert backend.autotune(ours, (), force=False) == {"block_sizes": [1, 1]}
+    del ours.config_spec
+    with pytest.raises(UnsupportedOperationError, match="no config"):
+        backend.autotune(ours, ())
+    assert callable(backend.get_do_bench()) and callable(backend.get_interleaved_bench())
     other_backend = types.SimpleNamespace(name="triton")
     assert fake_helion.BoundKernel(_softmax_kernel, other_backend).compile_config({}) == "helion-original"
     assert inject.install() is True  # idempotent
