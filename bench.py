@@ -156,6 +156,7 @@ class Workload:
     dtype = ""
     bound = "tensor"
     scaling = "weak"  # per-GPU work is fixed as N grows ("strong": total work is fixed)
+    collective = False  # the step holds a collective: every rank must run every call of it
     traffic: float | None = None  # DRAM bytes per launch of the dominant kernel (ncu, profiles/)
 
     def setup(self, device: torch.device, rank: int) -> None:
@@ -602,6 +603,7 @@ class ColumnShardedLinear(Workload):
 
     name, metric, unit, dtype, bound = "c2n_column_sharded_linear_8192x4096x4096", "bf16 GEMM TFLOP/s", "TFLOP/s", "bf16", "tensor"
     scaling = "strong"
+    collective = True
     M, N, K, SETS = 8192, 4096, 4096, 3
     fused = False
 
@@ -943,10 +945,21 @@ def main() -> None:
                            "exchange_ms_per_step": max(device_ms - g_ms, 0.0) / args.steps,
                            "exchange_share": max(device_ms - g_ms, 0.0) / device_ms,
                            "note": "local GEMM of this rank's columns timed alone; the remainder of the step is the exchange"}
+        # A step can be no faster than the slower of this rank's FLOPs at the measured GEMM peak
+        # and the bytes it must send over NVLink at the measured peer-copy rate (770 GB/s per
+        # direction per GPU on this pool): the shard, once to every other rank.
+        flops_ms = workload.work_per_step() / (harness.peaks["bf16_tflops"] * 1e12) * 1e3
+        link_bytes = 2.0 * workload.M * (workload.N / world) * (world - 1)
+        link_ms = link_bytes / 770e9 * 1e3
+        floor_ms = max(flops_ms, link_ms)
+        extras["roofline_exchange"] = {"bound": "tensor" if flops_ms >= link_ms else "nvlink", "flops_ms": flops_ms,
+                                       "nvlink_ms": link_ms, "nvlink_bytes_out_per_rank": link_bytes,
+                                       "nvlink_gbs_assumed": 770.0, "floor_ms": floor_ms,
+                                       "frac": floor_ms / (device_ms / args.steps)}
 
     status = native.kernel_status(device)
     parity: dict[str, object] = {}
-    if rank == 0:
+    if rank == 0 or workload.collective:
         try:
             parity = workload.parity()
         except Exception as exc:

@@ -31,6 +31,7 @@ SOURCES = [
     "gemm_umma.cu",
     "host_rows.cu",
     "attention.cu",
+    "peer.cu",
 ]
 HEADERS = ["common.cuh", "gemm_common.cuh", "umma_ptx.cuh", "../../include/b200ops.h"]
 FLAGS = [

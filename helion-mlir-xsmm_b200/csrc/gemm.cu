@@ -18,8 +18,6 @@
 
 namespace b200 {
 
-int umma_supports(const b200_gemm_desc& d);
-int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* partials, cudaStream_t stream);
 int explain_gemm_umma(const b200_gemm_desc& d, char* buf, size_t len);
 int run_wait_timeout_selftest(unsigned long long budget_ns, cudaStream_t stream);
 int run_gemm_simt(const b200_gemm_desc& d, const GemmOperand& a, const GemmOperand& b, const GemmEpilogue& epi,
@@ -350,6 +348,45 @@ extern "C" int b200_gemm(const b200_gemm_desc* desc, void* stream) {
     return run_gemm_umma(u, r.epi, partials, s);
   }
   return run_gemm_umma(d, r.epi, partials, s);
+}
+
+// The GEMM of b200_gemm with its result stored into `out->count` copies of C: this GPU's
+// (desc->c, which must be out->c[out->rank]) and its peers' (device pointers into their
+// memory, mapped here). Tensor-core path only (bf16 operands in plain layouts, one
+// problem, no split-K): refused otherwise, never run another way.
+extern "C" int b200_gemm_to_peers(const b200_gemm_desc* desc, const b200_peer_out* out, void* stream) {
+  if (!enabled()) return refuse(B200_E_DISABLED);
+  if (!out) return refuse(B200_E_NULL);
+  Resolved r{};
+  const int bad = validate(desc, &r);
+  if (bad) return refuse(bad);
+  const b200_gemm_desc& d = *desc;
+  if (out->count < 1 || out->count > B200_MAX_PEERS || out->rank < 0 || out->rank >= out->count) return refuse(B200_E_ARG);
+  if (!out->done_counter || !aligned(out->done_counter, 4)) return refuse(B200_E_NULL);
+  for (int j = 0; j < out->count; ++j)
+    if (!out->c[j] || !out->flags[j] || !aligned(out->flags[j], 4)) return refuse(B200_E_NULL);
+  if (out->c[out->rank] != d.c) return refuse(B200_E_ARG);
+  if (d.m == 0 || d.n == 0 || d.k == 0) return refuse(B200_E_SHAPE);  // the flags are only raised by a launch
+  if (d.batch != 1 || d.split_k > 1) return refuse(B200_E_ARG);
+  if (device_info().sm_count == 0) return refuse(B200_E_DEVICE);
+  int why = 0;
+  if (choose(d, r, &why) != kPathUmma) return refuse(why ? why : B200_E_ARG);
+  PeerOut peers{};
+  peers.count = out->count;
+  peers.epoch = out->epoch;
+  for (int j = 0; j < out->count; ++j) {
+    peers.delta[j] = static_cast<int64_t>(reinterpret_cast<intptr_t>(out->c[j]) - reinterpret_cast<intptr_t>(d.c));
+    peers.flags[j] = out->flags[j];
+  }
+  peers.done_counter = out->done_counter;
+  return run_gemm_umma(d, r.epi, nullptr, static_cast<cudaStream_t>(stream), &peers);
+}
+
+extern "C" int b200_peer_wait(const int32_t* flags, int32_t count, int32_t epoch, uint64_t budget_ns, void* stream) {
+  if (!enabled()) return refuse(B200_E_DISABLED);
+  if (!flags) return refuse(B200_E_NULL);
+  if (count < 1 || count > B200_MAX_PEERS || budget_ns == 0 || budget_ns > 10000000000ull) return refuse(B200_E_ARG);
+  return run_peer_wait(flags, count, epoch, budget_ns, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int b200_gemm_explain(const b200_gemm_desc* desc, char* buf, size_t buf_len) {

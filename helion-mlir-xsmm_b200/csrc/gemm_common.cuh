@@ -65,6 +65,24 @@ __device__ __forceinline__ int64_t offset_b(const GemmOperand& b, int64_t k, int
   }
 }
 
+// Destinations of a GEMM whose result goes to every GPU of a group (the fused form of a
+// column-sharded linear followed by an all-gather): the epilogue stores each finished
+// piece of C into every copy through peer pointers (plain stores over NVLink; operands
+// are only ever loaded from this GPU's own memory), and when the last CTA has stored, one
+// flag per destination says so.
+struct PeerOut {
+  int32_t count;           // copies of C, this GPU's own included
+  int32_t epoch;           // value written to the flags
+  int64_t delta[8];        // byte offset from this GPU's C to copy j
+  int32_t* flags[8];       // word on GPU j that this GPU's kernel sets to `epoch` when its stores are done
+  uint32_t* done_counter;  // on this GPU: CTAs that have finished (reset by the last one)
+};
+
+int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* partials, cudaStream_t stream,
+                  const PeerOut* peers = nullptr);
+int umma_supports(const b200_gemm_desc& d);
+int run_peer_wait(const int32_t* flags, int count, int32_t epoch, unsigned long long budget_ns, cudaStream_t stream);
+
 // One f32 operand to be widened into its six-fold bf16 split (split_f32_kernel, pack.cu).
 struct SplitOperand {
   const float* src;

@@ -46,7 +46,8 @@ constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccStride = 256;  // TMEM columns between the two accumulators
 
 // Status bits (also reported through b200_read_kernel_status).
-constexpr int kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueWait = 4, kErrDrainWait = 8, kErrSelfTest = 16;
+constexpr int kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueWait = 4, kErrDrainWait = 8, kErrSelfTest = 16,
+              kErrPeerWait = 32;
 
 struct UmmaParams {
   int32_t m, n, k, batch;
@@ -71,6 +72,8 @@ struct UmmaParams {
   int32_t vec_store;   // rows of C are 16-byte aligned
   int32_t vec_params;  // bias / scale / shift start on 16-byte boundaries
   int32_t* status;
+  PeerOut peer;  // PEERS instantiation only: the copies of C on this and the other GPUs
+  int32_t peer_staged;  // PEERS: results go through shared memory and leave as whole 128-byte lines
 };
 
 struct __align__(8) PipelineBarriers {
@@ -182,7 +185,42 @@ __device__ __forceinline__ void activate32(int act, float alpha, float (&v)[32])
   }
 }
 
-template <int CG>
+// One rounding and the store of 32 consecutive columns (col0..) of one row of C
+// (16-byte stores when the rows allow).
+__device__ __forceinline__ void store32(const UmmaParams& p, uint8_t* c_row, int64_t col0, bool full_chunk,
+                                        const float (&v)[32]) {
+  if (p.out_bf16) {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(c_row) + col0;
+    if (full_chunk && p.vec_store) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 q;
+        q.x = pack_bf16x2(v[8 * j], v[8 * j + 1]);
+        q.y = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
+        q.z = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]);
+        q.w = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
+        *reinterpret_cast<uint4*>(dst + 8 * j) = q;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.n) dst[j] = __float2bfloat16_rn(v[j]);
+    }
+  } else {
+    float* dst = reinterpret_cast<float*>(c_row) + col0;
+    if (full_chunk && p.vec_store) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<float4*>(dst + 4 * j) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.n) dst[j] = v[j];
+    }
+  }
+}
+
+template <int CG, bool PEERS = false>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_umma_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                           const UmmaParams p) {
@@ -369,6 +407,81 @@ __global__ void __launch_bounds__(kThreads, 1)
         tc_fence_after();
         const bool last = s == p.splits - 1;
         const int c_begin = half * half_cols, c_end = (half + 1) * half_cols;
+        if constexpr (PEERS) {
+          // Stores that cross NVLink should be whole 128-byte lines: a thread's own 16-byte
+          // pieces of its row (the direct form below) travel as separate small writes (measured
+          // on two GPUs: 33.5 MB to the peer in 180 us, a quarter of the link's rate). So the bf16
+          // results of 64 columns go through a per-warp tile in shared memory (32 rows x 128
+          // bytes, 16-byte pieces XOR-swizzled by row so that neither side conflicts) and leave
+          // row-major: eight lanes write one row's 128 bytes, a warp four rows per instruction.
+          if (p.peer_staged && static_cast<int64_t>(t.n0) + c_end <= p.n) {
+            uint8_t* stage = smem_aligned + static_cast<size_t>(p.stages) * stage_bytes + 1024 + warp * 4096;
+            const int64_t row0 = static_cast<int64_t>(t.m0) + quarter * 32;
+            uint8_t* c_tile = static_cast<uint8_t*>(p.c) + row0 * p.ldc * 2;  // batch 1, no parallel splits
+            for (int c0 = c_begin; c0 < c_end; c0 += 64) {
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                uint32_t raw[32];
+                tmem_ld_32x32(tmem_base + lane_base + acc * kAccStride + c0 + 32 * h, raw);
+                tmem_ld_wait();
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+                const int64_t col0 = static_cast<int64_t>(t.n0) + c0 + 32 * h;
+                const bool vec_fast = p.vec_params != 0;
+                if (p.epi.bias) {
+                  float w[32];
+                  load_vec32(p.epi.bias, col0, p.n, p.epi.vec_bf16, p.epi.bias_scalar, vec_fast, w);
+#pragma unroll
+                  for (int j = 0; j < 32; ++j) v[j] += w[j];
+                }
+                if (p.epi.scale) {
+                  float w[32];
+                  load_vec32(p.epi.scale, col0, p.n, p.epi.vec_bf16, p.epi.scale_scalar, vec_fast, w);
+#pragma unroll
+                  for (int j = 0; j < 32; ++j) v[j] *= w[j];
+                }
+                if (p.epi.shift) {
+                  float w[32];
+                  load_vec32(p.epi.shift, col0, p.n, p.epi.vec_bf16, p.epi.shift_scalar, vec_fast, w);
+#pragma unroll
+                  for (int j = 0; j < 32; ++j) v[j] += w[j];
+                }
+                activate32(p.epi.act, p.epi.alpha, v);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  uint4 q;
+                  q.x = pack_bf16x2(v[8 * j], v[8 * j + 1]);
+                  q.y = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
+                  q.z = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]);
+                  q.w = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
+                  *reinterpret_cast<uint4*>(stage + lane * 128 + (((4 * h + j) ^ (lane & 7)) << 4)) = q;
+                }
+              }
+              __syncwarp();
+              const int piece = lane & 7;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int r = 4 * i + (lane >> 3);
+                const uint4 q = *reinterpret_cast<const uint4*>(stage + r * 128 + ((piece ^ (r & 7)) << 4));
+                if (row0 + r < p.m) {
+                  uint8_t* to = c_tile + static_cast<int64_t>(r) * p.ldc * 2 + (static_cast<int64_t>(t.n0) + c0) * 2 + piece * 16;
+                  for (int dest = 0; dest < p.peer.count; ++dest) *reinterpret_cast<uint4*>(to + p.peer.delta[dest]) = q;
+                }
+              }
+              __syncwarp();
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+              if (CG == 2)
+                mbar_arrive_leader(smem_u32(&bars->acc_empty[acc]));
+              else
+                mbar_arrive(smem_u32(&bars->acc_empty[acc]));
+            }
+            continue;
+          }
+        }
         for (int c0 = c_begin; c0 < c_end; c0 += 32) {
           uint32_t raw[32];
           tmem_ld_32x32(tmem_base + lane_base + acc * kAccStride + c0, raw);
@@ -432,34 +545,11 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             activate32(p.epi.act, p.epi.alpha, v);
           }
-          if (p.out_bf16) {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(c_row) + col0;
-            if (full_chunk && p.vec_store) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                uint4 q;
-                q.x = pack_bf16x2(v[8 * j], v[8 * j + 1]);
-                q.y = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
-                q.z = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]);
-                q.w = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
-                *reinterpret_cast<uint4*>(dst + 8 * j) = q;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.n) dst[j] = __float2bfloat16_rn(v[j]);
-            }
+          if constexpr (PEERS) {
+            // the same piece into every copy of C (this GPU's and its peers')
+            for (int dest = 0; dest < p.peer.count; ++dest) store32(p, c_row + p.peer.delta[dest], col0, full_chunk, v);
           } else {
-            float* dst = reinterpret_cast<float*>(c_row) + col0;
-            if (full_chunk && p.vec_store) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                *reinterpret_cast<float4*>(dst + 4 * j) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.n) dst[j] = v[j];
-            }
+            store32(p, c_row, col0, full_chunk, v);
           }
         }
         // This warp has read the whole accumulator: hand it back to the MMA warp
@@ -481,6 +571,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   // ------------------------------------------------------------------ teardown
   // Neither CTA of a pair may leave while the other can still read its shared
   // memory (MMA operands) or signal its barriers.
+  if constexpr (PEERS) {
+    if (warp < kEpilogueWarps) __threadfence_system();  // this thread's stores, before the CTA reports
+  }
   tc_fence_before();
   if (CG == 2)
     cluster_sync_all();
@@ -489,6 +582,40 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc<CG>(tmem_base, kTmemCols);
+  }
+  if constexpr (PEERS) {
+    // The last CTA to get here has seen every other CTA's report, each made after that
+    // CTA's stores were fenced: it resets the counter for the next launch and raises this
+    // GPU's flag on every destination.
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      const uint32_t earlier = atomicAdd(p.peer.done_counter, 1u);
+      if (earlier + 1 == gridDim.x) {
+        __threadfence_system();
+        atomicExch(p.peer.done_counter, 0u);
+        for (int dest = 0; dest < p.peer.count; ++dest)
+          asm volatile("st.release.sys.global.b32 [%0], %1;" ::"l"(p.peer.flags[dest]), "r"(p.peer.epoch) : "memory");
+      }
+    }
+  }
+}
+
+// Waits until every flag of `flags[0..count)` (set by the kernels above, one per GPU of
+// the group) has reached `epoch`, or gives up after `budget_ns` and leaves kErrPeerWait in
+// the status word. One thread per flag.
+__global__ void peer_wait_kernel(const int32_t* flags, int count, int32_t epoch, unsigned long long budget_ns,
+                                 int32_t* status) {
+  if (static_cast<int>(threadIdx.x) >= count) return;
+  const int32_t* flag = flags + threadIdx.x;
+  const unsigned long long start = global_ns();
+  for (uint32_t spin = 0;; ++spin) {
+    int32_t seen;
+    asm volatile("ld.acquire.sys.global.b32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+    if (seen - epoch >= 0) return;
+    if ((spin & 63u) == 63u && global_ns() - start > budget_ns) {
+      if (status) atomicOr(status, kErrPeerWait);
+      return;
+    }
   }
 }
 
@@ -648,14 +775,15 @@ int64_t tail_batches(const b200_gemm_desc& d, const UmmaPlan& plan, int sm_count
   return peel;
 }
 
-int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* partials, cudaStream_t stream) {
+int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* partials, cudaStream_t stream,
+                  const PeerOut* peers) {
   const DeviceInfo& dev = device_info();
   if (dev.sm_count == 0) return refuse(B200_E_DEVICE);
   const bool a_kmajor = d.a_layout == B200_LAYOUT_ROW;  // [M,K]: K contiguous
   const bool b_kmajor = d.b_layout == B200_LAYOUT_COL;  // [N,K]: K contiguous
   const bool parallel = partials != nullptr && d.split_k > 1;
   const UmmaPlan plan = umma_plan(d, dev.sm_count, parallel);
-  if (const int64_t peel = parallel ? 0 : tail_batches(d, plan, dev.sm_count)) {
+  if (const int64_t peel = (parallel || peers) ? 0 : tail_batches(d, plan, dev.sm_count)) {
     b200_gemm_desc head = d, tail = d;
     head.batch = d.batch - peel;
     head.tile_n = -256;  // fixed widths: neither part is planned (or peeled) again
@@ -665,9 +793,9 @@ int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* parti
     tail.a = static_cast<const uint8_t*>(d.a) + head.batch * d.stride_a * 2;
     tail.b = static_cast<const uint8_t*>(d.b) + head.batch * d.stride_b * 2;
     tail.c = static_cast<uint8_t*>(d.c) + head.batch * d.stride_c * out_size;
-    int rc = run_gemm_umma(head, epi, nullptr, stream);
+    int rc = run_gemm_umma(head, epi, nullptr, stream, nullptr);
     if (rc != 0) return rc;
-    rc = run_gemm_umma(tail, epi, nullptr, stream);
+    rc = run_gemm_umma(tail, epi, nullptr, stream, nullptr);
     if (rc == 0) counters().calls.fetch_sub(1, std::memory_order_relaxed);  // one call, two launches
     return rc;
   }
@@ -731,16 +859,38 @@ int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* parti
                 (p.psplit_stride * out_size) % 16 == 0;
   p.vec_params = aligned(epi.bias, 16) && aligned(epi.scale, 16) && aligned(epi.shift, 16);
   p.status = kernel_status_word();
+  size_t smem_bytes = plan.smem;
+  if (peers) {
+    if (parallel || plan.splits > 1) return refuse(B200_E_ARG);  // one launch, one epilogue per tile
+    p.peer = *peers;
+    for (int j = 0; j < peers->count; ++j)  // every copy must take the same kind of stores
+      p.vec_store = p.vec_store && (peers->delta[j] % 16 == 0);
+    // Staged stores (see the epilogue): bf16 results, 16-byte aligned rows, column halves in
+    // whole 64-column pieces. The eight 4 KiB staging tiles take the place of pipeline stages.
+    if (p.out_bf16 && p.vec_store && (plan.block_n / 2) % 64 == 0) {
+      const size_t stage = static_cast<size_t>(p.a_stage_bytes) + p.b_stage_bytes;
+      const size_t staging = static_cast<size_t>(kEpilogueWarps) * 4096;
+      while (p.stages > 2 && stage * p.stages + 1024 + sizeof(PipelineBarriers) + 1024 + staging > size_t(227) * 1024) --p.stages;
+      smem_bytes = stage * p.stages + 1024 + sizeof(PipelineBarriers) + 1024 + staging;
+      p.peer_staged = smem_bytes <= size_t(227) * 1024;
+      if (!p.peer_staged) {
+        p.stages = plan.stages;
+        smem_bytes = plan.smem;
+      }
+    }
+  }
 
   std::call_once(g_attr_once[dev.device], [] {
     cudaFuncSetAttribute(gemm_umma_bf16_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     cudaFuncSetAttribute(gemm_umma_bf16_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaFuncSetAttribute(gemm_umma_bf16_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaFuncSetAttribute(gemm_umma_bf16_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
   });
   if (plan.cta_group == 2) {
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(plan.grid);
     config.blockDim = dim3(kThreads);
-    config.dynamicSmemBytes = plan.smem;
+    config.dynamicSmemBytes = smem_bytes;
     config.stream = stream;
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeClusterDimension;
@@ -749,19 +899,29 @@ int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* parti
     attr.val.clusterDim.z = 1;
     config.attrs = &attr;
     config.numAttrs = 1;
-    const cudaError_t err = cudaLaunchKernelEx(&config, gemm_umma_bf16_kernel<2>, map_a, map_b, p);
+    const cudaError_t err = peers ? cudaLaunchKernelEx(&config, gemm_umma_bf16_kernel<2, true>, map_a, map_b, p)
+                                  : cudaLaunchKernelEx(&config, gemm_umma_bf16_kernel<2>, map_a, map_b, p);
     if (err != cudaSuccess) {
       cudaGetLastError();
       return finish(-static_cast<int>(err));
     }
   } else {
-    gemm_umma_bf16_kernel<1><<<plan.grid, kThreads, plan.smem, stream>>>(map_a, map_b, p);
+    if (peers)
+      gemm_umma_bf16_kernel<1, true><<<plan.grid, kThreads, smem_bytes, stream>>>(map_a, map_b, p);
+    else
+      gemm_umma_bf16_kernel<1><<<plan.grid, kThreads, smem_bytes, stream>>>(map_a, map_b, p);
   }
   if (!parallel) return launched();
   const int rc = check_launch();
   if (rc != 0) return finish(rc);
   return launch_splitk_reduce(partials, plan.psplits, d.batch, d.m, d.n, d.c, d.out_dtype == B200_BF16, d.ldc,
                               d.stride_c, epi, stream);
+}
+
+int run_peer_wait(const int32_t* flags, int count, int32_t epoch, unsigned long long budget_ns, cudaStream_t stream) {
+  if (device_info().sm_count == 0) return refuse(B200_E_DEVICE);
+  peer_wait_kernel<<<1, 32, 0, stream>>>(flags, count, epoch, budget_ns, kernel_status_word());
+  return launched();
 }
 
 int run_wait_timeout_selftest(unsigned long long budget_ns, cudaStream_t stream) {

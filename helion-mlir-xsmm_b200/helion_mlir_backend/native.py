@@ -109,6 +109,24 @@ class PoolStats(ctypes.Structure):
     _fields_ = [(name, c_uint64) for name in ("hits", "misses", "free_blocks", "free_bytes", "max_bytes", "live_blocks", "live_bytes")]
 
 
+MAX_PEERS = 8
+IPC_HANDLE_BYTES = 64
+
+
+class PeerOut(ctypes.Structure):
+    """``b200_peer_out``: the copies of C of a GEMM stored to every GPU of a group."""
+
+    _fields_ = [
+        ("count", c_int32),
+        ("rank", c_int32),
+        ("epoch", c_int32),
+        ("reserved_", c_int32),
+        ("c", c_void_p * MAX_PEERS),
+        ("flags", c_void_p * MAX_PEERS),
+        ("done_counter", c_void_p),
+    ]
+
+
 class Counters(ctypes.Structure):
     _fields_ = [
         ("launches", c_uint64),
@@ -166,6 +184,12 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "b200_column_sum_static": (c_int, [c_int32, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "b200_column_sum_static_fits": (c_int, [c_int64, c_int64, c_size_t]),
     "b200_eltwise": (c_int, [c_int32, c_int32, c_void_p, c_void_p, c_int64, c_float, c_void_p]),
+    "b200_gemm_to_peers": (c_int, [ctypes.POINTER(GemmDesc), ctypes.POINTER(PeerOut), c_void_p]),
+    "b200_peer_wait": (c_int, [c_void_p, c_int32, c_int32, c_uint64, c_void_p]),
+    "b200_symm_alloc": (c_int, [c_size_t, ctypes.POINTER(c_void_p), c_void_p]),
+    "b200_symm_open": (c_int, [c_void_p, ctypes.POINTER(c_void_p)]),
+    "b200_symm_close": (c_int, [c_void_p]),
+    "b200_symm_free": (c_int, [c_void_p]),
     "b200_pool_alloc": (c_int, [c_size_t, c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_int32)]),
     "b200_pool_free": (c_int, [c_void_p, c_void_p]),
     "b200_pool_set_limit": (c_int, [c_size_t]),

@@ -307,6 +307,46 @@ typedef struct b200_counters_t {
 int b200_get_counters(b200_counters_t* out);
 int b200_reset_counters(void);
 
+/* ---- column-sharded linear with the all-gather fused into the GEMM ----
+ *
+ * No counterpart in the reference (one process, one CPU). A linear layer whose
+ * weight is split along N over the G GPUs of a box computes its columns of y on
+ * each GPU; every GPU needs all of y. Instead of a GEMM followed by an NCCL
+ * all-gather, b200_gemm_to_peers stores each finished piece of its columns into all
+ * G copies of y (plain stores through peer pointers over NVLink while the tensor
+ * cores work on the next tile), and when its last CTA has stored it raises one flag
+ * word on every GPU. b200_peer_wait, enqueued after it, returns when all G flags
+ * of this GPU have been raised: y is then complete here.
+ *
+ * Memory: the copies of y and the flag words must be mapped in every rank's
+ * process: b200_symm_alloc (cudaMalloc + zero fill + an IPC handle to send to the
+ * other ranks, e.g. through torch.distributed), b200_symm_open (maps a peer's
+ * handle, enabling peer access), b200_symm_close / b200_symm_free. Operands (A, B,
+ * bias) are always read from the calling GPU's own memory.
+ *
+ * Waits are bounded: after `budget_ns` b200_peer_wait gives up, ORs 32 into the
+ * kernel status word and returns; nothing hangs if a peer never arrives. A rank must
+ * not start a GEMM into a copy of y that a peer may still be reading: alternate two
+ * buffers and keep each rank's calls in stream order (helion_mlir_utils.sharding). */
+#define B200_MAX_PEERS 8
+#define B200_IPC_HANDLE_BYTES 64
+typedef struct b200_peer_out {
+  int32_t count;                   /* G: copies of C, this GPU's included */
+  int32_t rank;                    /* index of this GPU's own copy: c[rank] == desc->c */
+  int32_t epoch;                   /* value the flags are set to (increase it per call) */
+  int32_t reserved_;
+  void* c[B200_MAX_PEERS];         /* where C starts in copy j (device pointers valid on this GPU) */
+  int32_t* flags[B200_MAX_PEERS];  /* the word on GPU j that this GPU raises */
+  uint32_t* done_counter;          /* a zeroed word on this GPU, private to these calls */
+} b200_peer_out;
+int b200_gemm_to_peers(const b200_gemm_desc* desc, const b200_peer_out* out, void* stream);
+/* Waits (on the device, `stream` order) until flags[0..count) have all reached `epoch`. */
+int b200_peer_wait(const int32_t* flags, int32_t count, int32_t epoch, uint64_t budget_ns, void* stream);
+int b200_symm_alloc(size_t bytes, void** out_ptr, void* out_handle /* B200_IPC_HANDLE_BYTES */);
+int b200_symm_open(const void* handle /* B200_IPC_HANDLE_BYTES */, void** out_ptr);
+int b200_symm_close(void* ptr);
+int b200_symm_free(void* ptr);
+
 /* Device error word written by kernels whose bounded waits ran out
  * (0 = none). Reading it synchronises the given stream. */
 int b200_read_kernel_status(void* stream, int32_t* out_status);

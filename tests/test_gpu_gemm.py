@@ -358,3 +358,24 @@ def test_f32_widened_product_long_sums(ops, positive: bool) -> None:
     assert checks.rel_frobenius(ops.matmul(da, db).cpu(), ref.matmul(a, b)) <= 1e-5
     a3, b3 = make(1536, 2048), make(2048, 1536)
     assert checks.rel_frobenius(ops.matmul(*cuda(a3, b3)).cpu(), ref.matmul(a3, b3)) <= 1e-5
+
+
+def test_peer_wait_gives_up_and_reports() -> None:
+    """The device-side wait that ends a fused column-sharded linear, on a flag nobody raises:
+    it runs out after its budget, leaves bit 32 in the status word, and the context stays
+    usable. A flag that is already raised lets it through at once."""
+    from helion_mlir_backend import native
+
+    lib = native.module()
+    torch.cuda.synchronize()
+    assert native.kernel_status() == 0
+    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    stream = native.stream_ptr(flags.device)
+    assert lib.b200_peer_wait(flags.data_ptr(), 2, 1, 2_000_000, stream) == 0  # 2 ms
+    assert native.kernel_status() == 32
+    flags.fill_(3)
+    assert lib.b200_peer_wait(flags.data_ptr(), 8, 3, 2_000_000, stream) == 0
+    assert native.kernel_status() == 0
+    assert lib.b200_peer_wait(flags.data_ptr(), 9, 1, 2_000_000, stream) == 7
+    assert lib.b200_peer_wait(None, 2, 1, 2_000_000, stream) == 6
+    assert lib.b200_peer_wait(flags.data_ptr(), 2, 1, 0, stream) == 7

@@ -1,5 +1,6 @@
 """What needs two GPUs on one box: the column-sharded linear over NCCL (the one exchange
-the operator set has) and the allocation-free column sum on a device other than 0.
+the operator set has) and its fused form (epilogue stores into every rank's copy of y through peer memory, flag words, bounded
+wait), and the allocation-free column sum on a device other than 0.
 Skipped on a single-GPU machine; the host logic of the exchange is also covered on CPU
 by two gloo ranks (tests/test_sharding_gloo.py)."""
 
@@ -38,6 +39,22 @@ expect = ref.linear(data["x"], data["w"], data["b"], F.gelu)
 checks.assert_parity(torch.bfloat16, y.cpu(), expect, f"rank {{rank}} column-sharded linear")
 whole = ops.matmul(x, data["w"].cuda(), trans_b=True, bias=data["b"].cuda(), epilogue=F.gelu)
 assert torch.equal(y, whole), "the gathered shards are the unsharded result, bit for bit"
+# the fused form: every rank's epilogue stores its columns into all copies of y over peer memory
+from helion_mlir_backend import native
+fused = sharding.FusedColumnShardedLinear(1024, 768, 512, torch.bfloat16, torch.device("cuda", rank))
+for call in range(5):  # the two copies of y alternate
+    yf = fused(x, w, b, F.gelu)
+    torch.cuda.synchronize()
+    assert torch.equal(yf, whole), f"fused call {{call}} on rank {{rank}}"
+assert native.kernel_status() == 0, "a bounded wait ran out"
+# back to back without host synchronisation, results used in stream order
+acc = torch.zeros(1024, 768, device="cuda")
+for call in range(6):
+    acc += fused(x, w, b, F.gelu).float()
+torch.cuda.synchronize()
+assert torch.equal(acc, whole.float() * 6)
+assert native.kernel_status() == 0
+fused.close()
 # ragged shares (770 columns over 2 ranks would be equal; 771 is not): the general gather
 data = inputs.c2_linear(m=256, n=771, k=256)
 n0, n1 = sharding.shard_bounds(771, world, rank)
