@@ -2,9 +2,9 @@
 //
 // Paths, in order of preference:
 //   tensor cores  bf16 operands whose rows TMA can describe (16-byte aligned bases
-//                 and pitches), plain ROW/COL layouts directly; blocked A and the
-//                 blocked / VNNI layouts of B through unpacks to row-major in the
-//                 caller's workspace
+//                 and pitches), plain ROW/COL layouts and 32x32-blocked A directly (the
+//                 blocks are what a 5-D tensor map walks); the blocked / VNNI layouts of B
+//                 through one unpack to K-contiguous rows in the caller's workspace
 //                 f32 operands (plain or 32x32-blocked, batched or not) as a six-term
 //                 bf16 split over a 6x longer K
 //   FFMA          everything else (small or oddly pitched f32, explicit f32 split-K), exact f32
@@ -50,7 +50,6 @@ struct Resolved {
   int64_t n_pad;        // N as the packed B layout pads it
   bool b_is_vnni;
   int64_t m_pad;          // M as the blocked A layout pads it
-  size_t unpack_a_bytes;  // workspace for a blocked A unpacked to [m_pad, k_pad] bf16
   size_t unpack_bytes;    // workspace for a packed B unpacked to [n_pad, k_pad] bf16
   size_t partial_bytes; // workspace for parallel split-K partials
   size_t split_a_bytes, split_b_bytes;  // workspace for the six-fold bf16 split of f32 operands (0: not applicable)
@@ -158,8 +157,6 @@ int validate(const b200_gemm_desc* d, Resolved* r) {
   r->b_is_vnni = d->b_layout == B200_LAYOUT_BLOCKED_VNNI || d->b_layout == B200_LAYOUT_VNNI_PANELS;
   r->m_pad = round_up(d->m, 32);
   const bool bf16 = d->dtype == B200_BF16;
-  r->unpack_a_bytes =
-      (bf16 && d->a_layout == B200_LAYOUT_BLOCKED) ? static_cast<size_t>(round_up(r->m_pad * k32 * 2, 256)) : 0;
   r->unpack_bytes = (bf16 && d->b_layout >= B200_LAYOUT_BLOCKED)
                         ? static_cast<size_t>(round_up(r->n_pad * k32 * 2, 256))
                         : 0;
@@ -182,14 +179,8 @@ int validate(const b200_gemm_desc* d, Resolved* r) {
 
 // The descriptor the tensor-core kernel sees once packed operands have been
 // unpacked: A as row-major [m_pad, k_pad], B as K-contiguous [n_pad, k_pad].
-b200_gemm_desc unpacked_desc(const b200_gemm_desc& d, const Resolved& r, void* a_unpacked, void* b_unpacked) {
+b200_gemm_desc unpacked_desc(const b200_gemm_desc& d, const Resolved& r, void* b_unpacked) {
   b200_gemm_desc u = d;
-  if (r.unpack_a_bytes) {
-    u.a = a_unpacked;
-    u.a_layout = B200_LAYOUT_ROW;
-    u.lda = r.k_pad;
-    u.stride_a = r.m_pad * r.k_pad;
-  }
   if (r.unpack_bytes) {
     u.b = b_unpacked;
     u.b_layout = B200_LAYOUT_COL;
@@ -253,17 +244,17 @@ Path choose(const b200_gemm_desc& d, const Resolved& r, int* why) {
   *why = 0;
   if (d.force_kernel == 2) return kPathSimt;
   if (d.k == 0) return kPathSimt;
-  if (r.unpack_a_bytes || r.unpack_bytes) {
+  if (r.unpack_bytes) {
     if (d.batch != 1) {
       *why = B200_E_SHAPE;
       return kPathSimt;
     }
-    if (!d.workspace || d.workspace_bytes < r.unpack_a_bytes + r.unpack_bytes || !aligned(d.workspace, 256)) {
+    if (!d.workspace || d.workspace_bytes < r.unpack_bytes || !aligned(d.workspace, 256)) {
       *why = B200_E_WORKSPACE;
       return kPathSimt;
     }
     uint8_t* ws = static_cast<uint8_t*>(d.workspace);
-    b200_gemm_desc u = unpacked_desc(d, r, ws, ws + r.unpack_a_bytes);
+    b200_gemm_desc u = unpacked_desc(d, r, ws);
     *why = umma_supports(u);
     return *why == 0 ? kPathUmmaUnpack : kPathSimt;
   }
@@ -288,7 +279,7 @@ using namespace b200;
 extern "C" size_t b200_gemm_workspace_bytes(const b200_gemm_desc* desc) {
   Resolved r{};
   if (validate(desc, &r) != 0 || desc->m == 0 || desc->n == 0) return 0;
-  return r.unpack_a_bytes + r.unpack_bytes + r.partial_bytes + r.split_a_bytes + r.split_b_bytes + r.split_partial_bytes;
+  return r.unpack_bytes + r.partial_bytes + r.split_a_bytes + r.split_b_bytes + r.split_partial_bytes;
 }
 
 extern "C" int b200_gemm(const b200_gemm_desc* desc, void* stream) {
@@ -307,12 +298,11 @@ extern "C" int b200_gemm(const b200_gemm_desc* desc, void* stream) {
   // Workspace carve-up: [unpacked A][unpacked B][split-K partials].
   uint8_t* ws = static_cast<uint8_t*>(d.workspace);
   size_t ws_left = d.workspace ? d.workspace_bytes : 0;
-  void *a_unpacked = nullptr, *b_unpacked = nullptr;
+  void* b_unpacked = nullptr;
   if (path == kPathUmmaUnpack) {
-    a_unpacked = ws;
-    b_unpacked = ws + r.unpack_a_bytes;
-    ws += r.unpack_a_bytes + r.unpack_bytes;
-    ws_left -= r.unpack_a_bytes + r.unpack_bytes;
+    b_unpacked = ws;
+    ws += r.unpack_bytes;
+    ws_left -= r.unpack_bytes;
   }
   float* partials = nullptr;
   if (d.split_k > 1 && ws_left >= r.partial_bytes && ws_left > 0 && aligned(ws, 16)) partials = reinterpret_cast<float*>(ws);
@@ -332,11 +322,6 @@ extern "C" int b200_gemm(const b200_gemm_desc* desc, void* stream) {
   }
 
   if (path == kPathUmmaUnpack) {
-    if (r.unpack_a_bytes) {
-      const int rc =
-          b200_pack(B200_UNPACK_A_BLOCKED_TO_MK, B200_BF16, d.a, 0, 0, 0, a_unpacked, r.m_pad, r.k_pad, 0, stream);
-      if (rc != 0) return rc;
-    }
     if (r.unpack_bytes) {
       const int kind = d.b_layout == B200_LAYOUT_VNNI_PANELS  ? B200_UNPACK_B_VNNI_PANELS_TO_NK
                        : d.b_layout == B200_LAYOUT_BLOCKED_VNNI ? B200_UNPACK_B_VNNI_TO_NK
@@ -344,7 +329,7 @@ extern "C" int b200_gemm(const b200_gemm_desc* desc, void* stream) {
       const int rc = b200_pack(kind, B200_BF16, d.b, 0, 0, 0, b_unpacked, r.n_pad, r.k_pad, d.b_panel, stream);
       if (rc != 0) return rc;
     }
-    const b200_gemm_desc u = unpacked_desc(d, r, a_unpacked, b_unpacked);
+    const b200_gemm_desc u = unpacked_desc(d, r, b_unpacked);
     return run_gemm_umma(u, r.epi, partials, s);
   }
   return run_gemm_umma(d, r.epi, partials, s);
@@ -407,12 +392,12 @@ extern "C" int b200_gemm_explain(const b200_gemm_desc* desc, char* buf, size_t b
   }
   uint8_t* ws = static_cast<uint8_t*>(desc->workspace);
   b200_gemm_desc u = *desc;
-  if (path == kPathUmmaUnpack) u = unpacked_desc(*desc, r, ws, ws ? ws + r.unpack_a_bytes : nullptr);
+  if (path == kPathUmmaUnpack) u = unpacked_desc(*desc, r, ws);
   if (path == kPathUmmaSplitF32) u = split_desc(*desc, ws, ws + r.split_a_bytes);
   char inner[200];
   explain_gemm_umma(u, inner, sizeof inner);
   snprintf(buf, buf_len, "%s%s",
-           path == kPathUmmaUnpack     ? "unpack to row-major + "
+           path == kPathUmmaUnpack     ? "unpack B to K-contiguous rows + "
            : path == kPathUmmaSplitF32 ? "f32 as 6 bf16 cross products (K x6) + "
                                        : "",
            inner);

@@ -65,6 +65,7 @@ struct UmmaParams {
   // matrix descriptor constants: high word and leading-byte-offset field
   uint32_t a_desc_hi, b_desc_hi, a_desc_lbo, b_desc_lbo;
   uint32_t a_kstep, b_kstep;  // descriptor start-address advance (16-byte units) per UMMA K step
+  uint32_t a_khalf;           // ... from the first to the third K step of a stage (see umma_bf16_x4_peek)
   GemmEpilogue epi;
   void* c;
   int64_t ldc, stride_c;
@@ -220,7 +221,7 @@ __device__ __forceinline__ void store32(const UmmaParams& p, uint8_t* c_row, int
   }
 }
 
-template <int CG, bool PEERS = false>
+template <int CG, bool PEERS = false, bool A_BLOCKED = false>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_umma_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                           const UmmaParams p) {
@@ -298,7 +299,15 @@ __global__ void __launch_bounds__(kThreads, 1)
               else
                 tma_load_3d(dst, map, full, c0, c1, t.batch);
             };
-            if (p.a_kmajor) {
+            if constexpr (A_BLOCKED) {
+              // two K blocks of four row blocks each: 128 rows x 64 bytes, 8 KiB apart
+              for (int j = 0; j < 2; ++j) {
+                if (CG == 2)
+                  tma_load_5d_pair(a_dst + j * 8192, &map_a, full, 0, 0, (k0 >> 5) + j, t.m0 >> 5, t.batch);
+                else
+                  tma_load_5d(a_dst + j * 8192, &map_a, full, 0, 0, (k0 >> 5) + j, t.m0 >> 5, t.batch);
+              }
+            } else if (p.a_kmajor) {
               load(a_dst, &map_a, k0, t.m0);
             } else {
               for (int j = 0; j < kBlockM / 64; ++j) load(a_dst + j * 8192, &map_a, t.m0 + 64 * j, k0);
@@ -374,8 +383,12 @@ __global__ void __launch_bounds__(kThreads, 1)
               parity ^= 1u;
             }
             // (after the last block of the last tile the tested barrier is simply never armed again)
-            landed = umma_bf16_x4_peek<CG>(d_tmem, a_desc, b_desc, p.a_kstep, p.b_kstep, p.idesc, accumulate,
-                                           smem_u32(&bars->full[stage]), parity) != 0;
+            if constexpr (A_BLOCKED)
+              landed = umma_bf16_x4_peek<CG, true>(d_tmem, a_desc, b_desc, p.a_kstep, p.b_kstep, p.idesc, accumulate,
+                                                   smem_u32(&bars->full[stage]), parity, p.a_khalf) != 0;
+            else
+              landed = umma_bf16_x4_peek<CG>(d_tmem, a_desc, b_desc, p.a_kstep, p.b_kstep, p.idesc, accumulate,
+                                             smem_u32(&bars->full[stage]), parity) != 0;
             accumulate = 1;
             umma_commit<CG>(smem_u32(&bars->empty[this_stage]));
           }
@@ -655,9 +668,10 @@ std::once_flag g_attr_once[64];
 // The strides TMA needs: 16-byte aligned bases and row pitches.
 int umma_supports(const b200_gemm_desc& d) {
   if (d.dtype != B200_BF16) return B200_E_DTYPE;
-  if (d.a_layout > B200_LAYOUT_COL || d.b_layout > B200_LAYOUT_COL) return B200_E_ARG;
+  const bool a_blocked = d.a_layout == B200_LAYOUT_BLOCKED;  // read in place through a 5-D tensor map
+  if ((d.a_layout > B200_LAYOUT_COL && !a_blocked) || d.b_layout > B200_LAYOUT_COL) return B200_E_ARG;
   if (!aligned(d.a, 16) || !aligned(d.b, 16)) return B200_E_ALIGN;
-  if (d.lda % 8 || d.ldb % 8 || (d.batch > 1 && (d.stride_a % 8 || d.stride_b % 8))) return B200_E_STRIDE;
+  if ((!a_blocked && d.lda % 8) || d.ldb % 8 || (d.batch > 1 && (d.stride_a % 8 || d.stride_b % 8))) return B200_E_STRIDE;
   if (d.m > INT32_MAX - 256 || d.n > INT32_MAX - 256 || d.k > INT32_MAX - 256 || d.batch > 65535)
     return B200_E_SHAPE;
   if (d.k < 1) return B200_E_SHAPE;
@@ -779,7 +793,7 @@ int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* parti
                   const PeerOut* peers) {
   const DeviceInfo& dev = device_info();
   if (dev.sm_count == 0) return refuse(B200_E_DEVICE);
-  const bool a_kmajor = d.a_layout == B200_LAYOUT_ROW;  // [M,K]: K contiguous
+  const bool a_kmajor = d.a_layout == B200_LAYOUT_ROW || d.a_layout == B200_LAYOUT_BLOCKED;  // K contiguous
   const bool b_kmajor = d.b_layout == B200_LAYOUT_COL;  // [N,K]: K contiguous
   const bool parallel = partials != nullptr && d.split_k > 1;
   const UmmaPlan plan = umma_plan(d, dev.sm_count, parallel);
@@ -802,7 +816,11 @@ int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* parti
 
   CUtensorMap map_a, map_b;
   bool ok;
-  if (a_kmajor)
+  const bool a_blocked = d.a_layout == B200_LAYOUT_BLOCKED;
+  if (a_blocked) {
+    const int64_t mb = round_up(d.m, 32) / 32, kb = round_up(d.k, 32) / 32;
+    ok = encode_map_blocked(&map_a, d.a, mb, kb, d.batch, d.batch > 1 ? d.stride_a : mb * kb * 1024, kBlockM / 32);
+  } else if (a_kmajor)
     ok = encode_map(&map_a, d.a, d.k, d.m, d.batch, d.lda, d.batch > 1 ? d.stride_a : d.lda * d.m, kStageK, kBlockM);
   else
     ok = encode_map(&map_a, d.a, d.m, d.k, d.batch, d.lda, d.batch > 1 ? d.stride_a : d.lda * d.k, 64, kStageK);
@@ -834,12 +852,15 @@ int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* parti
   p.b_stage_bytes = static_cast<uint32_t>(plan.block_n / plan.cta_group) * 128;  // this CTA's share of the B tile
   // K-major: 8-row groups 1024 B apart, K step = 32 B inside the swizzled row.
   // MN-major: 8-k-row groups 1024 B apart (SBO), 64-column chunks 8 KiB apart (LBO), K step = 16 rows = 2 KiB.
-  p.a_desc_hi = desc_hi(1024);
+  // Blocked A: rows of 64 bytes (one 32-wide K block) under the 64-byte swizzle, 8-row groups
+  // 512 B apart; the stage's second K block starts 8 KiB (128 rows) further on.
+  p.a_desc_hi = a_blocked ? desc_hi(512, 4) : desc_hi(1024);
   p.b_desc_hi = desc_hi(1024);
   p.a_desc_lbo = a_kmajor ? 1u : (8192u >> 4);
   p.b_desc_lbo = b_kmajor ? 1u : (8192u >> 4);
   p.a_kstep = a_kmajor ? (32u >> 4) : (2048u >> 4);
   p.b_kstep = b_kmajor ? (32u >> 4) : (2048u >> 4);
+  p.a_khalf = a_blocked ? (8192u >> 4) : 2 * p.a_kstep;
   if (parallel) {
     p.epi = GemmEpilogue{};
     p.c = partials;
@@ -861,7 +882,7 @@ int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* parti
   p.status = kernel_status_word();
   size_t smem_bytes = plan.smem;
   if (peers) {
-    if (parallel || plan.splits > 1) return refuse(B200_E_ARG);  // one launch, one epilogue per tile
+    if (parallel || plan.splits > 1 || a_blocked) return refuse(B200_E_ARG);  // one launch, one epilogue per tile; plain A
     p.peer = *peers;
     for (int j = 0; j < peers->count; ++j)  // every copy must take the same kind of stores
       p.vec_store = p.vec_store && (peers->delta[j] % 16 == 0);
@@ -885,6 +906,8 @@ int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* parti
     cudaFuncSetAttribute(gemm_umma_bf16_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     cudaFuncSetAttribute(gemm_umma_bf16_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     cudaFuncSetAttribute(gemm_umma_bf16_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaFuncSetAttribute(gemm_umma_bf16_kernel<1, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaFuncSetAttribute(gemm_umma_bf16_kernel<2, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
   });
   if (plan.cta_group == 2) {
     cudaLaunchConfig_t config = {};
@@ -899,8 +922,9 @@ int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* parti
     attr.val.clusterDim.z = 1;
     config.attrs = &attr;
     config.numAttrs = 1;
-    const cudaError_t err = peers ? cudaLaunchKernelEx(&config, gemm_umma_bf16_kernel<2, true>, map_a, map_b, p)
-                                  : cudaLaunchKernelEx(&config, gemm_umma_bf16_kernel<2>, map_a, map_b, p);
+    const cudaError_t err = peers       ? cudaLaunchKernelEx(&config, gemm_umma_bf16_kernel<2, true>, map_a, map_b, p)
+                            : a_blocked ? cudaLaunchKernelEx(&config, gemm_umma_bf16_kernel<2, false, true>, map_a, map_b, p)
+                                        : cudaLaunchKernelEx(&config, gemm_umma_bf16_kernel<2>, map_a, map_b, p);
     if (err != cudaSuccess) {
       cudaGetLastError();
       return finish(-static_cast<int>(err));
@@ -908,6 +932,8 @@ int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* parti
   } else {
     if (peers)
       gemm_umma_bf16_kernel<1, true><<<plan.grid, kThreads, smem_bytes, stream>>>(map_a, map_b, p);
+    else if (a_blocked)
+      gemm_umma_bf16_kernel<1, false, true><<<plan.grid, kThreads, smem_bytes, stream>>>(map_a, map_b, p);
     else
       gemm_umma_bf16_kernel<1><<<plan.grid, kThreads, smem_bytes, stream>>>(map_a, map_b, p);
   }

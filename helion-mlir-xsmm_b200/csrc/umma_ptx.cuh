@@ -83,6 +83,14 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+// 5-D form (32x32-blocked operands: k, m, k block, m block, batch).
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int32_t c0, int32_t c1,
+                                            int32_t c2, int32_t c3, int32_t c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+      : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -135,6 +143,13 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap
       ::"r"(dst), "l"(map), "r"(bar & kLeaderMask), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_5d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int32_t c0,
+                                                 int32_t c1, int32_t c2, int32_t c3, int32_t c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar & kLeaderMask), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+      : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 template <int CG>
@@ -165,12 +180,16 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint
 // core idles for every cycle the issuing thread spends between blocks). Returns
 // whether the tested phase had completed. `first_accumulate`: 0 overwrites the
 // accumulator with the first product.
-template <int CG>
+// `a_half` > 0: the descriptor distance from the first to the third K slice of A when the
+// stage is not one contiguous run of slices (the second 32-wide K block of a 32x32-blocked
+// operand); 0: four slices `a_step` apart. A compile-time choice of the caller: the plain
+// form must not pay for the other in the issue loop.
+template <int CG, bool A_SPLIT = false>
 __device__ __forceinline__ uint32_t umma_bf16_x4_peek(uint32_t d_tmem, uint64_t a0, uint64_t b0, uint64_t a_step,
                                                       uint64_t b_step, uint32_t idesc, uint32_t first_accumulate,
-                                                      uint32_t peek_bar, uint32_t peek_parity) {
+                                                      uint32_t peek_bar, uint32_t peek_parity, uint64_t a_half = 0) {
   uint32_t ready;
-  const uint64_t a1 = a0 + a_step, a2 = a1 + a_step, a3 = a2 + a_step;
+  const uint64_t a1 = a0 + a_step, a2 = A_SPLIT ? a0 + a_half : a1 + a_step, a3 = a2 + a_step;
   const uint64_t b1 = b0 + b_step, b2 = b1 + b_step, b3 = b2 + b_step;
   if (CG == 1)
     asm volatile(
@@ -346,8 +365,29 @@ bool encode_map(CUtensorMap* map, const void* base, int64_t cols, int64_t rows, 
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// High word of a matrix descriptor: stride byte offset, version 1, 128-byte swizzle.
-__host__ __device__ inline uint32_t desc_hi(uint32_t sbo_bytes) { return (sbo_bytes >> 4) | (1u << 14) | (2u << 29); }
+// 5-D map over a 32x32-blocked bf16 operand [batch][rows/32][cols/32][32][32] (row-major
+// blocks), 64-byte swizzle: a box is `box_blocks` row blocks of one column block, i.e.
+// 32 * box_blocks rows of 64 bytes, contiguous in shared memory.
+bool encode_map_blocked(CUtensorMap* map, const void* base, int64_t row_blocks, int64_t col_blocks, int64_t batch,
+                        int64_t batch_stride, uint32_t box_blocks) {
+  EncodeTiled fn = encode_tiled();
+  if (!fn) return false;
+  const cuuint64_t dims[5] = {32, 32, static_cast<cuuint64_t>(col_blocks), static_cast<cuuint64_t>(row_blocks),
+                              static_cast<cuuint64_t>(batch)};
+  const cuuint64_t strides[4] = {64, 2048, static_cast<cuuint64_t>(col_blocks) * 2048,
+                                 static_cast<cuuint64_t>(batch_stride) * 2};
+  const cuuint32_t box[5] = {32, 32, 1, box_blocks, 1};
+  const cuuint32_t elem[5] = {1, 1, 1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// High word of a matrix descriptor: stride byte offset, version 1, swizzle mode
+// (2: 128-byte rows, 4: 64-byte rows).
+__host__ __device__ inline uint32_t desc_hi(uint32_t sbo_bytes, uint32_t swizzle_mode = 2) {
+  return (sbo_bytes >> 4) | (1u << 14) | (swizzle_mode << 29);
+}
 
 }  // namespace
 }  // namespace b200

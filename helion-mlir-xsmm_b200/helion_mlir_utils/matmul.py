@@ -24,7 +24,9 @@ from __future__ import annotations
 
 from collections import OrderedDict
 import ctypes
+import os
 import threading
+import weakref
 from typing import TYPE_CHECKING
 from typing import Callable
 
@@ -820,9 +822,9 @@ def matmul_prepacked_b_affine(
 
 
 def unpack_b_to_nk(b4: Tensor) -> Tensor:
-    """A VNNI-packed bf16 right-hand side (panels ``[N/P, K/2, P, 2]`` or blocks
-    ``[N/32, K/32, 16, 32, 2]``) as the K-contiguous ``[N_pad, K_pad]`` matrix the
-    tensor cores read in place."""
+    """A packed bf16 right-hand side (VNNI panels ``[N/P, K/2, P, 2]``, VNNI blocks
+    ``[N/32, K/32, 16, 32, 2]`` or plain blocks ``[N/32, K/32, 32, 32]``) as the
+    K-contiguous ``[N_pad, K_pad]`` matrix the tensor cores read in place."""
     device = native.require_cuda(b4)
     b4 = b4.contiguous()
     if b4.dtype != torch.bfloat16:
@@ -832,8 +834,10 @@ def unpack_b_to_nk(b4: Tensor) -> Tensor:
         n_pad, k_pad, kind = panels * panel, 2 * pairs, native.UNPACK_B_VNNI_PANELS_TO_NK
     elif b4.dim() == 5 and tuple(b4.shape[2:]) == (16, 32, 2):
         n_pad, k_pad, kind, panel = int(b4.shape[0]) * 32, int(b4.shape[1]) * 32, native.UNPACK_B_VNNI_TO_NK, 0
+    elif b4.dim() == 4 and tuple(b4.shape[2:]) == (BLOCK_K, BLOCK_N):
+        n_pad, k_pad, kind, panel = int(b4.shape[0]) * 32, int(b4.shape[1]) * 32, native.UNPACK_B_BLOCKED_TO_NK, 0
     else:
-        raise ValueError(f"unpack_b_to_nk() expects a VNNI-packed tensor, got {tuple(b4.shape)}")
+        raise ValueError(f"unpack_b_to_nk() expects a packed right-hand side, got {tuple(b4.shape)}")
     out = output_pool.empty((n_pad, k_pad), dtype=b4.dtype, device=device)
     with native.on_device(device):
         code = native.module().b200_pack(
@@ -976,13 +980,55 @@ def matmul_blocked(
     key = ("blocked", m, n, k, a4.dtype, device, layout, _tensor_key(b4), _tensor_key(bias), _tensor_key(scale_v),
            _tensor_key(shift_v), out_dtype, epilogue)
 
+    # A packed bf16 right-hand side is a weight: its K-contiguous form, which the tensor
+    # cores read in place, is made once and kept while the packed tensor lives unchanged
+    # (the left-hand side is an activation and is read as it comes).
+    ldb = 0
+    if a4.dtype == torch.bfloat16 and _keep_prepared_weights():
+        b4, layout, ldb = _unpacked_rhs(b4), native.LAYOUT_COL, kb * 32
+        key = key + ("nk",)
+
     def build() -> GemmPlan:
         return _plan_gemm(
-            a=a4, m=m, n=n, k=k, a_layout=native.LAYOUT_BLOCKED, b_layout=layout, lda=0, ldb=0,
+            a=a4, m=m, n=n, k=k, a_layout=native.LAYOUT_BLOCKED, b_layout=layout, lda=0, ldb=ldb,
             bias=bias, scale=scale_v, shift=shift_v, epilogue=epilogue, out_dtype=out_dtype,
         )
 
     return _cached_plan(key, build).run(a4, b4, bias, scale_v, shift_v)
+
+
+# id(packed tensor) -> (weak reference to it, its version when unpacked, the unpacked form).
+# Keyed by identity (tensors do not compare as keys); an entry goes when its tensor dies.
+_UNPACKED_RHS: dict[int, tuple["weakref.ref[Tensor]", int, Tensor]] = {}
+_UNPACKED_RHS_LOCK = threading.Lock()
+
+
+def _keep_prepared_weights() -> bool:
+    """Whether prepared forms of constant weights are kept between calls: the switch of
+    ``linear.cache_prepacked_weights`` (``HELION_MLIR_CACHE_PREPACKED_WEIGHTS=0`` prepares
+    them on every call; linear.py:25-33 of the reference)."""
+    value = os.environ.get("HELION_MLIR_CACHE_PREPACKED_WEIGHTS")
+    return value is None or value.strip().lower() not in {"0", "false", "no", "off"}
+
+
+def _unpacked_rhs(b4: Tensor) -> Tensor:
+    """The K-contiguous form of the packed right-hand side ``b4``, remembered per tensor
+    object and redone when the tensor was written to (its ``_version`` moved). A change
+    through ``.data`` is not seen, as for the weight cache of :func:`linear`."""
+    key = id(b4)
+    with _UNPACKED_RHS_LOCK:
+        hit = _UNPACKED_RHS.get(key)
+        if hit is not None and hit[0]() is b4 and hit[1] == b4._version:
+            return hit[2]
+    unpacked = unpack_b_to_nk(b4)
+
+    def forget(_: object, key: int = key) -> None:
+        with _UNPACKED_RHS_LOCK:
+            _UNPACKED_RHS.pop(key, None)
+
+    with _UNPACKED_RHS_LOCK:
+        _UNPACKED_RHS[key] = (weakref.ref(b4, forget), b4._version, unpacked)
+    return unpacked
 
 
 # --------------------------------------------------------------------------- batched

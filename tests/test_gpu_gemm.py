@@ -379,3 +379,39 @@ def test_peer_wait_gives_up_and_reports() -> None:
     assert lib.b200_peer_wait(flags.data_ptr(), 9, 1, 2_000_000, stream) == 7
     assert lib.b200_peer_wait(None, 2, 1, 2_000_000, stream) == 6
     assert lib.b200_peer_wait(flags.data_ptr(), 2, 1, 0, stream) == 7
+
+
+def test_blocked_a_is_read_in_place_also_batched(ops) -> None:
+    """A [M/32, K/32, 32, 32] (matmul.py:92-99) reaches the tensor cores through a 5-D tensor
+    map: no unpack pass, no scratch, and a batch of blocked operands stays on the same kernel
+    (C ABI; ragged M and an odd number of K blocks included)."""
+    from helion_mlir_backend import native
+
+    lib = native.module()
+    gen = torch.Generator().manual_seed(31)
+    batch, m, n, k = 3, 200, 144, 160  # 7 row blocks, 5 K blocks: the last stage is half empty
+    a, b = rand(gen, batch, m, k), rand(gen, batch, k, n, scale=0.25)
+    a4 = torch.stack([ref.pack_a_blocked(a[i]) for i in range(batch)]).contiguous()
+    da, db = cuda(a4, b)
+    out = torch.full((batch, m, n), float("nan"), dtype=F32, device="cuda")
+    desc = native.GemmDesc()
+    desc.dtype, desc.out_dtype, desc.vec_dtype = native.BF16, native.F32, native.BF16
+    desc.a_layout, desc.b_layout = native.LAYOUT_BLOCKED, native.LAYOUT_ROW
+    desc.m, desc.n, desc.k, desc.batch = m, n, k, batch
+    desc.lda, desc.ldb, desc.ldc = 0, n, n
+    desc.stride_a, desc.stride_b, desc.stride_c = a4[0].numel(), k * n, m * n
+    desc.a, desc.b, desc.c = da.data_ptr(), db.data_ptr(), out.data_ptr()
+    buf = ctypes.create_string_buffer(256)
+    assert lib.b200_gemm_explain(ctypes.byref(desc), buf, len(buf)) == 0
+    text = buf.value.decode()
+    assert text.startswith("umma_bf16") and "unpack" not in text, text
+    assert lib.b200_gemm_workspace_bytes(ctypes.byref(desc)) == 0
+    rc = lib.b200_gemm(ctypes.byref(desc), native.stream_ptr(da.device))
+    assert rc == 0, native.strerror(rc)
+    expect = torch.stack([ref.matmul(a[i], b[i], out_dtype=F32) for i in range(batch)])
+    assert checks.rel_frobenius(out.cpu(), expect) < 1e-5
+    # through the operator: the explanation of the blocked call names no unpack of A
+    m2, n2, k2 = 300, 200, 96
+    a2, b2 = rand(gen, m2, k2), rand(gen, k2, n2)
+    out2 = ops.matmul_blocked(*cuda(ref.pack_a_blocked(a2), ref.pack_b_blocked(b2)), m2, n2, k2)
+    checks.assert_parity(BF16, out2.cpu(), ref.matmul(a2, b2), "blocked a4 x b4")
