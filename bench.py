@@ -193,6 +193,9 @@ class Workload:
         """Kernels per step when they do not pass the library's launch counter (graph replays)."""
         return None
 
+    def teardown(self) -> None:
+        """Gives back what setup() took beyond tensors (collective where setup() was)."""
+
 
 def _rotating(count: int, make):
     return [make(i) for i in range(count)]
@@ -636,6 +639,11 @@ class ColumnShardedLinear(Workload):
             return self.ops.matmul(x, self.w, trans_b=True, bias=self.b, epilogue=F.gelu)
         return self.sharding.column_sharded_linear(x, self.w, self.b, self.N, F.gelu)
 
+    def teardown(self) -> None:
+        if self.fused_call is not None:
+            self.fused_call.close()
+            self.fused_call = None
+
     def gemm_only(self, index: int) -> torch.Tensor:
         return self.ops.matmul(self.xs[index % self.SETS], self.w, trans_b=True, bias=self.b, epilogue=F.gelu)
 
@@ -789,6 +797,64 @@ class Harness:
                 "peak_source": f"{self.peak_kind} ({what})", "traffic": workload.traffic}
 
 
+def host_copy_ceiling(harness: Harness, nbytes: int = 64 << 20, rounds: int = 8) -> dict[str, object]:
+    """What the box's host side can move with every rank copying at once: each rank copies
+    `nbytes` of pinned memory to its GPU and as much back, on two streams at the same time
+    (plain cudaMemcpyAsync through torch, one copy per direction per round). The end-to-end
+    leg can be no faster than its bytes over this rate."""
+    device = harness.device
+    up_src, down_dst = torch.empty(nbytes, dtype=torch.uint8).pin_memory(), torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    up_dst, down_src = torch.empty(nbytes, dtype=torch.uint8, device=device), torch.zeros(nbytes, dtype=torch.uint8, device=device)
+    up, down = torch.cuda.Stream(device), torch.cuda.Stream(device)
+    start, stop_up, stop_down = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+
+    def run(count: int) -> float:
+        harness.barrier()
+        start.record()
+        up.wait_event(start)
+        down.wait_event(start)
+        for _ in range(count):
+            with torch.cuda.stream(up):
+                up_dst.copy_(up_src, non_blocking=True)
+            with torch.cuda.stream(down):
+                down_dst.copy_(down_src, non_blocking=True)
+        stop_up.record(up)
+        stop_down.record(down)
+        harness.barrier()
+        up.synchronize()
+        down.synchronize()
+        return max(start.elapsed_time(stop_up), start.elapsed_time(stop_down))
+
+    run(2)
+    ms = harness.max_over_ranks(run(rounds))[0]
+    per_rank = nbytes * rounds / (ms * 1e-3) / 1e9
+    return {"per_rank_gbs_each_direction": per_rank, "aggregate_gbs_each_direction": per_rank * harness.world,
+            "how": f"{harness.world} ranks at once, {rounds} x {nbytes >> 20} MiB pinned host -> device and as much back concurrently, slowest rank"}
+
+
+def exchange_details(workload: "ColumnShardedLinear", harness: Harness, step_ms: float, steps: int) -> dict[str, object]:
+    """Where a column-sharded step's time goes (the local GEMM timed alone; the rest is the
+    exchange) and the floor it is held against: a step can be no faster than the slower of
+    this rank's FLOPs at the measured GEMM peak and the bytes it must send over NVLink (its
+    shard, once to every other rank) at the measured peer-copy rate of this pool, 770 GB/s per
+    direction per GPU."""
+    g_ms, _, _ = harness.timed(workload.gemm_only, steps)
+    g_ms /= steps
+    world = harness.world
+    flops_ms = workload.work_per_step() / (harness.peaks["bf16_tflops"] * 1e12) * 1e3
+    link_bytes = 2.0 * workload.M * (workload.N / world) * (world - 1)
+    link_ms = link_bytes / 770e9 * 1e3
+    floor_ms = max(flops_ms, link_ms)
+    return {
+        "split": {"gemm_ms_per_step": g_ms, "exchange_ms_per_step": max(step_ms - g_ms, 0.0),
+                  "exchange_share": max(step_ms - g_ms, 0.0) / step_ms,
+                  "note": "local GEMM of this rank's columns timed alone; the remainder of the step is the exchange"},
+        "roofline_exchange": {"bound": "tensor" if flops_ms >= link_ms else "nvlink", "flops_ms": flops_ms,
+                              "nvlink_ms": link_ms, "nvlink_bytes_out_per_rank": link_bytes, "nvlink_gbs_assumed": 770.0,
+                              "floor_ms": floor_ms, "frac": floor_ms / step_ms},
+    }
+
+
 def run_block(key: str, harness: Harness, rank: int, with_cpu: bool) -> dict[str, object]:
     """One of the other configurations: set up, warm up, size the inner repeat count from a
     pilot so that the timed region is BLOCK_TARGET_MS of device time, time it, check parity."""
@@ -831,7 +897,9 @@ def run_block(key: str, harness: Harness, rank: int, with_cpu: bool) -> dict[str
             block["e2e"] = {"value": 2.0 * workload.M * workload.N * 4 * 5 * harness.world / (e2e_ms * 1e-3) / 1e9,
                             "unit": "GB/s", "what": "stream_rows(softmax) f32 through pinned host buffers",
                             "h2d_bytes_per_step": e2e[0], "d2h_bytes_per_step": e2e[1], "ms_per_step": e2e_ms / 5}
-    if rank == 0:
+    if isinstance(workload, ColumnShardedLinear):
+        block.update(exchange_details(workload, harness, ms / repeats, 50))
+    if rank == 0 or workload.collective:
         try:
             block.update(workload.parity())
         except Exception as exc:  # a parity leg that cannot run is a failed parity, not a crashed benchmark
@@ -839,6 +907,7 @@ def run_block(key: str, harness: Harness, rank: int, with_cpu: bool) -> dict[str
         if with_cpu:
             block["cpu_baseline"] = cpu_baseline(workload, os.cpu_count() or 1, budget_s=3.0)
     harness.barrier()
+    workload.teardown()
     del workload
     from helion_mlir_utils import host_io
 
@@ -916,6 +985,7 @@ def main() -> None:
         h2d, d2h = first
         workload.e2e_step(1)
         e2e_ms, _, _ = harness.timed(workload.e2e_step, args.steps)
+    ceiling = host_copy_ceiling(harness) if first is not None else None
 
     main_only = args.only_main or args.workload != "c2"
     extras: dict[str, object] = {}
@@ -939,23 +1009,7 @@ def main() -> None:
         }
 
     if isinstance(workload, ColumnShardedLinear):
-        # where the step's time goes: the local GEMM alone, and the rest (the exchange)
-        g_ms, _, _ = harness.timed(workload.gemm_only, args.steps)
-        extras["split"] = {"gemm_ms_per_step": g_ms / args.steps,
-                           "exchange_ms_per_step": max(device_ms - g_ms, 0.0) / args.steps,
-                           "exchange_share": max(device_ms - g_ms, 0.0) / device_ms,
-                           "note": "local GEMM of this rank's columns timed alone; the remainder of the step is the exchange"}
-        # A step can be no faster than the slower of this rank's FLOPs at the measured GEMM peak
-        # and the bytes it must send over NVLink at the measured peer-copy rate (770 GB/s per
-        # direction per GPU on this pool): the shard, once to every other rank.
-        flops_ms = workload.work_per_step() / (harness.peaks["bf16_tflops"] * 1e12) * 1e3
-        link_bytes = 2.0 * workload.M * (workload.N / world) * (world - 1)
-        link_ms = link_bytes / 770e9 * 1e3
-        floor_ms = max(flops_ms, link_ms)
-        extras["roofline_exchange"] = {"bound": "tensor" if flops_ms >= link_ms else "nvlink", "flops_ms": flops_ms,
-                                       "nvlink_ms": link_ms, "nvlink_bytes_out_per_rank": link_bytes,
-                                       "nvlink_gbs_assumed": 770.0, "floor_ms": floor_ms,
-                                       "frac": floor_ms / (device_ms / args.steps)}
+        extras.update(exchange_details(workload, harness, device_ms / args.steps, args.steps))
 
     status = native.kernel_status(device)
     parity: dict[str, object] = {}
@@ -970,7 +1024,7 @@ def main() -> None:
     if not main_only:
         del workload.xs
         torch.cuda.empty_cache()
-        for key in BLOCKS:
+        for key in BLOCKS + (["c2n", "c2n_fused"] if world > 1 else []):
             blocks[key] = run_block(key, harness, rank, with_cpu=(world == 1 and not args.no_cpu_baseline and key == "c4"))
         status |= native.kernel_status(device)
 
@@ -996,6 +1050,11 @@ def main() -> None:
                 "value": work * args.steps * world / (e2e_ms * 1e-3) / scale, "unit": workload.unit,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps,
             }
+            if ceiling is not None:
+                # the step's larger transfer at the rate every rank gets when all copy both ways at once
+                floor_ms = max(h2d, d2h) / (float(ceiling["per_rank_gbs_each_direction"]) * 1e9) * 1e3
+                line["e2e"].update({"host_ceiling": ceiling, "floor_ms_per_step": floor_ms,
+                                    "frac_of_host_ceiling": floor_ms / (e2e_ms / args.steps)})
         else:
             line["e2e"] = None  # this workload has no host-buffer leg
         line.update(extras)
@@ -1004,6 +1063,7 @@ def main() -> None:
         if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = cpu_baseline(workload, os.cpu_count() or 1)
         print(json.dumps(line), flush=True)
+    workload.teardown()
     if distributed:
         dist.destroy_process_group()
 

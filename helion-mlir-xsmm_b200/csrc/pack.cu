@@ -358,46 +358,72 @@ __global__ void __launch_bounds__(256) unpack_b_blocked_kernel(const T* __restri
 // the column dimension of the logical matrix (copies side by side in a row, out
 // [batch][rows][6 * k_wide]); else the row dimension (out [batch][6 * k_wide][cols]).
 // k_wide >= the source's K: the rest of every copy is zero.
-__device__ __forceinline__ void split_one(const SplitOperand& o, int64_t i) {
+// A work item is eight consecutive elements of the widened operand's contiguous dimension
+// (whole 16-byte pieces of bf16 on the way out, two 16-byte loads on the way in when the
+// source allows).
+__device__ __forceinline__ void split_eight(const SplitOperand& o, int64_t item) {
   const int64_t lead = o.along_cols ? o.rows : o.k_wide, inner = o.along_cols ? o.k_wide : o.cols;
-  const int64_t per_batch = lead * inner;
-  const int64_t bi = i / per_batch, rem = i - bi * per_batch;
-  const int64_t r = rem / inner, c = rem - r * inner;
-  float x = 0.f;
+  const int64_t inner8 = inner >> 3;
+  const int64_t per_batch = lead * inner8;
+  const int64_t bi = item / per_batch, rem = item - bi * per_batch;
+  const int64_t r = rem / inner8, c = (rem - r * inner8) << 3;
+  float x[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) x[j] = 0.f;
   if (r < o.rows && c < o.cols) {
     const float* src = o.src + bi * o.batch_stride;
-    if (o.layout == 0)
-      x = src[r * o.ld + c];
-    else if (o.layout == 1)
-      x = src[(((r >> 5) * o.ld + (c >> 5)) << 10) + ((r & 31) << 5) + (c & 31)];
-    else
-      x = src[(((r >> 5) * o.ld + (c >> 5)) << 10) + ((c & 31) << 5) + (r & 31)];
+    if (o.layout == 2) {  // [rows/32][cols/32][32 c][32 r]: consecutive c are 32 elements apart
+      const float* at = src + (((r >> 5) * o.ld + (c >> 5)) << 10) + ((c & 31) << 5) + (r & 31);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (c + j < o.cols) x[j] = at[j << 5];
+    } else {
+      const float* at = o.layout == 0 ? src + r * o.ld + c : src + (((r >> 5) * o.ld + (c >> 5)) << 10) + ((r & 31) << 5) + (c & 31);
+      if (c + 8 <= o.cols && (reinterpret_cast<uintptr_t>(at) & 15) == 0) {
+        const float4 lo = *reinterpret_cast<const float4*>(at), hi = *reinterpret_cast<const float4*>(at + 4);
+        x[0] = lo.x, x[1] = lo.y, x[2] = lo.z, x[3] = lo.w, x[4] = hi.x, x[5] = hi.y, x[6] = hi.z, x[7] = hi.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (c + j < o.cols) x[j] = at[j];
+      }
+    }
   }
-  __nv_bfloat16 part[3];
-  part[0] = __float2bfloat16_rn(x);
-  const float r1 = x - __bfloat162float(part[0]);
-  part[1] = __float2bfloat16_rn(r1);
-  part[2] = __float2bfloat16_rn(r1 - __bfloat162float(part[1]));
+  // parts[t][j]: part t (0 largest) of element j, as bf16 bits
+  uint32_t packed[3][4];
+#pragma unroll
+  for (int j = 0; j < 8; j += 2) {
+    uint32_t bits[3][2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const __nv_bfloat16 p0 = __float2bfloat16_rn(x[j + e]);
+      const float r1 = x[j + e] - __bfloat162float(p0);
+      const __nv_bfloat16 p1 = __float2bfloat16_rn(r1);
+      const __nv_bfloat16 p2 = __float2bfloat16_rn(r1 - __bfloat162float(p1));
+      bits[0][e] = __bfloat16_as_ushort(p0), bits[1][e] = __bfloat16_as_ushort(p1), bits[2][e] = __bfloat16_as_ushort(p2);
+    }
+#pragma unroll
+    for (int t = 0; t < 3; ++t) packed[t][j >> 1] = bits[t][0] | (bits[t][1] << 16);
+  }
   const int pattern_a[6] = {2, 1, 0, 1, 0, 0}, pattern_b[6] = {0, 1, 2, 0, 1, 0};
-  __nv_bfloat16* dst = o.dst + bi * 6 * per_batch;
+  __nv_bfloat16* dst = o.dst + bi * 6 * lead * inner;
 #pragma unroll
   for (int t = 0; t < 6; ++t) {
-    const __nv_bfloat16 v = part[o.is_b ? pattern_b[t] : pattern_a[t]];
-    if (o.along_cols)
-      dst[r * (6 * inner) + t * inner + c] = v;
-    else
-      dst[(t * lead + r) * inner + c] = v;
+    const int part = o.is_b ? pattern_b[t] : pattern_a[t];
+    const uint4 q = make_uint4(packed[part][0], packed[part][1], packed[part][2], packed[part][3]);
+    __nv_bfloat16* to = o.along_cols ? dst + r * (6 * inner) + t * inner + c : dst + (t * lead + r) * inner + c;
+    *reinterpret_cast<uint4*>(to) = q;
   }
 }
 
-__global__ void __launch_bounds__(256) split_f32_kernel(const SplitOperand a, const SplitOperand b, int64_t total_a,
-                                                        int64_t total) {
+__global__ void __launch_bounds__(256) split_f32_kernel(const SplitOperand a, const SplitOperand b, int64_t items_a,
+                                                        int64_t items) {
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-    if (i < total_a)
-      split_one(a, i);
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < items; i += stride) {
+    if (i < items_a)
+      split_eight(a, i);
     else
-      split_one(b, i - total_a);
+      split_eight(b, i - items_a);
   }
 }
 
@@ -470,13 +496,15 @@ int run_pack(int kind, const PackParams& p, cudaStream_t stream) {
 
 // Widens both f32 operands of a GEMM into their six-fold bf16 splits (see split_f32_kernel).
 int launch_split_f32(const SplitOperand& a, const SplitOperand& b, cudaStream_t stream) {
+  // eight elements of the contiguous dimension per work item: that dimension (the widened K,
+  // or M / N of a [K, M] / [K, N] operand) is a multiple of 8 and the destinations 16-byte aligned
   auto count = [](const SplitOperand& o) {
-    return o.batch * (o.along_cols ? o.rows * o.k_wide : o.k_wide * o.cols);
+    return o.batch * (o.along_cols ? o.rows * (o.k_wide >> 3) : o.k_wide * (o.cols >> 3));
   };
-  const int64_t total_a = count(a), total = total_a + count(b);
-  const int64_t wanted = ceil_div(total, 256), resident = static_cast<int64_t>(device_info().sm_count) * 16;
+  const int64_t items_a = count(a), items = items_a + count(b);
+  const int64_t wanted = ceil_div(items, 256), resident = static_cast<int64_t>(device_info().sm_count) * 16;
   const unsigned grid = static_cast<unsigned>(wanted < resident ? (wanted > 0 ? wanted : 1) : resident);
-  split_f32_kernel<<<grid, 256, 0, stream>>>(a, b, total_a, total);
+  split_f32_kernel<<<grid, 256, 0, stream>>>(a, b, items_a, items);
   return check_launch();
 }
 
