@@ -1,7 +1,7 @@
 """Benchmark of the hot path: the fused bf16 linear  y = GELU(x @ W^T + b), with the
 other four configurations of the baseline timed beside it in the same line.
 
-    python bench.py --gpus N --steps K --warmup W [--workload c2|c4|c1|c3|c5|attn|c2n]
+    python bench.py --gpus N --steps K --warmup W [--workload c2|c4|c1|c3|c5|attn|c2n|c2n_fused|kernels]
                     [--only-main] [--impl reference]
 
 A step is one pass of the hot path over one batch of synthetic input. The default
@@ -599,6 +599,87 @@ class Attention(Workload):
         return 4.0 * self.CPU_HEADS * self.S * self.S * self.D
 
 
+class BandwidthKernels(Workload):
+    """The bandwidth-bound kernel families beside C4's three: reductions, element-wise
+    operators, layout conversions, long-row softmax. One launch of each per step; the line's
+    `kernels` block times each alone (bytes read + written over the CUDA-event time)."""
+
+    name, metric, unit, dtype, bound = "bandwidth_kernels", "reduction / element-wise / pack HBM GB/s", "GB/s", "f32+bf16", "hbm"
+    only: str | None = None  # --kernel NAME: that one kernel only (profiler captures)
+
+    def setup(self, device: torch.device, rank: int) -> None:
+        import helion_mlir_utils as ops
+
+        self.ops, self.device = ops, device
+        gen = torch.Generator(device=device).manual_seed(1007 + rank)
+        m, n = 32768, 4096
+        x32 = torch.randn(m, n, generator=gen, device=device)
+        x16 = x32.bfloat16()
+        tall32 = torch.randn(1 << 20, 64, generator=gen, device=device)
+        tall16 = tall32.bfloat16()
+        v = torch.randn(n, generator=gen, device=device)
+        v16 = v.bfloat16().reshape(n, 1)
+        long32 = torch.randn(2048, 65536, generator=gen, device=device)
+        sq16 = torch.randn(8192, 8192, generator=gen, device=device).bfloat16()
+        sq32 = torch.randn(8192, 8192, generator=gen, device=device)
+        f4, f2 = 4.0 * m * n, 2.0 * m * n
+        t4, t2 = 4.0 * (1 << 20) * 64, 2.0 * (1 << 20) * 64
+        s2, s4 = 2.0 * 8192 * 8192, 4.0 * 8192 * 8192
+        # (name, bytes read + written, call)
+        self.items = [
+            ("row_sum_f32_32768x4096", f4, lambda: ops.row_sum(x32)),
+            ("row_sum_bf16_32768x4096", f2, lambda: ops.row_sum(x16)),
+            ("row_dot_f32_32768x4096", f4, lambda: ops.row_dot(x32, v)),
+            ("row_dot_bf16_32768x4096", f2, lambda: ops.row_dot(x16, v)),
+            ("matvec_bf16_32768x4096", f2, lambda: ops.matvec(x16, v16)),
+            ("column_sum_f32_32768x4096", f4, lambda: ops.column_sum(x32)),
+            ("column_sum_bf16_32768x4096", f2, lambda: ops.column_sum(x16)),
+            ("row_sum_f32_1048576x64", t4, lambda: ops.row_sum(tall32)),
+            ("row_sum_bf16_1048576x64", t2, lambda: ops.row_sum(tall16)),
+            ("column_sum_f32_1048576x64", t4, lambda: ops.column_sum(tall32)),
+            ("column_sum_bf16_1048576x64", t2, lambda: ops.column_sum(tall16)),
+            ("relu_f32_32768x4096", 2 * f4, lambda: ops.relu(x32)),
+            ("leaky_relu_bf16_32768x4096", 2 * f2, lambda: ops.leaky_relu(x16)),
+            ("scalar_mul_f32_32768x4096", 2 * f4, lambda: ops.scalar_mul(x32, 1.5)),
+            ("softmax_long_rows_f32_2048x65536", 2 * 4.0 * 2048 * 65536, lambda: ops.softmax(long32)),
+            ("pack_a_blocked_bf16_8192", 2 * s2, lambda: ops.pack_a_blocked(sq16)),
+            ("pack_a_blocked_t_bf16_8192", 2 * s2, lambda: ops.pack_a_blocked_t(sq16)),
+            ("pack_b_blocked_vnni_bf16_8192", 2 * s2, lambda: ops.pack_b_blocked_vnni(sq16)),
+            ("pack_b_blocked_t_f32_8192", 2 * s4, lambda: ops.pack_b_blocked_t(sq32)),
+            ("pack_b_vnni_t_bf16_8192", 2 * s2, lambda: ops.pack_b_vnni_t(sq16, 128)),
+        ]
+        if self.only:
+            self.items = [item for item in self.items if item[0] == self.only]
+            if not self.items:
+                raise SystemExit(f"--kernel {self.only}: no such kernel in this workload")
+
+    def step(self, index: int) -> torch.Tensor:
+        out = None
+        for _, _, call in self.items:
+            out = call()
+        return out
+
+    def work_per_step(self) -> float:
+        return float(sum(nbytes for _, nbytes, _ in self.items))
+
+    def config(self) -> dict[str, object]:
+        return {"workload": self.name, "kernels": [name for name, _, _ in getattr(self, "items", [])],
+                "l2": "every operand is 0.13-1 GiB, beyond the 126 MB L2"}
+
+    def parity(self) -> dict[str, object]:
+        return {"parity_metric": None, "parity_pass": None,
+                "checked": "these kernels are compared with the oracle and the fixtures by tests/test_gpu_golden.py, test_gpu_packs.py"}
+
+    def cpu_setup(self) -> str:
+        self.cpu = torch.randn(4096, 4096)
+        return "row sums, column sums and relu of 4096 of 32768 rows, torch CPU"
+
+    def cpu_step(self) -> float:
+        x = self.cpu
+        x.sum(1), x.sum(0), torch.relu(x)
+        return 4.0 * x.numel() * 4
+
+
 class ColumnShardedLinear(Workload):
     """C2-N: the C2 linear with W split along N over the ranks; every rank holds all of x,
     computes its columns of y and the column shards are all-gathered (NCCL) into the whole
@@ -682,7 +763,7 @@ class FusedColumnShardedLinear(ColumnShardedLinear):
 
 
 WORKLOADS = {"c1": F32Matmul, "c2": LinearGelu, "c3": BlockedMatmul, "c4": RowNorms, "c5": SplitKBmm, "attn": Attention,
-             "c2n": ColumnShardedLinear, "c2n_fused": FusedColumnShardedLinear}
+             "c2n": ColumnShardedLinear, "c2n_fused": FusedColumnShardedLinear, "kernels": BandwidthKernels}
 BLOCKS = ["c4", "c1", "c3", "c5"]  # timed beside the main line, in this order
 
 
@@ -924,6 +1005,7 @@ def main() -> None:
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     parser.add_argument("--rows", type=int, default=0, help="rows per GPU of the c2/c4 workloads, heads per GPU of attn, batches per GPU of c5 (default: the configuration's; smaller sizes are for profiler captures, not for reported numbers)")
+    parser.add_argument("--kernel", default=None, help="kernels workload: run this one kernel only (profiler captures)")
     parser.add_argument("--only-main", action="store_true", help="skip the blocks of the other configurations, the sustained leg and the linear() leg")
     parser.add_argument("--via-linear", action="store_true", help="c2: time linear(x, layer, F.gelu, cache) as the main step")
     parser.add_argument("--no-cpu-baseline", action="store_true")
@@ -939,6 +1021,8 @@ def main() -> None:
             if hasattr(workload, name):
                 setattr(workload, name, args.rows)
                 break
+    if isinstance(workload, BandwidthKernels):
+        workload.only = args.kernel
     if args.via_linear and isinstance(workload, LinearGelu):
         workload.via_linear = True
     if args.impl == "reference":
@@ -1010,6 +1094,13 @@ def main() -> None:
 
     if isinstance(workload, ColumnShardedLinear):
         extras.update(exchange_details(workload, harness, device_ms / args.steps, args.steps))
+    if isinstance(workload, BandwidthKernels):
+        table = {}
+        for name, nbytes, call in workload.items:
+            k_ms, _, _ = harness.timed(lambda i, call=call: call(), 20)
+            gbs = nbytes * 20 / (k_ms * 1e-3) / 1e9
+            table[name] = {"GB/s": round(gbs, 1), "frac": round(gbs / harness.peaks["hbm_gbs"], 3)}
+        extras["kernels"] = table
 
     status = native.kernel_status(device)
     parity: dict[str, object] = {}
