@@ -60,6 +60,7 @@ struct UmmaParams {
   int32_t block_n;
   int32_t stages;
   int32_t a_kmajor, b_kmajor;
+  int32_t a_chunked, b_chunked;  // an M- / N-contiguous operand whose 64-column chunks arrive in one 4-D copy
   uint32_t idesc;
   uint32_t a_stage_bytes, b_stage_bytes;
   // matrix descriptor constants: high word and leading-byte-offset field
@@ -309,11 +310,21 @@ __global__ void __launch_bounds__(kThreads, 1)
               }
             } else if (p.a_kmajor) {
               load(a_dst, &map_a, k0, t.m0);
+            } else if (p.a_chunked) {
+              if (CG == 2)
+                tma_load_4d_pair(a_dst, &map_a, full, 0, k0, t.m0 >> 6, t.batch);
+              else
+                tma_load_4d(a_dst, &map_a, full, 0, k0, t.m0 >> 6, t.batch);
             } else {
               for (int j = 0; j < kBlockM / 64; ++j) load(a_dst + j * 8192, &map_a, t.m0 + 64 * j, k0);
             }
             if (p.b_kmajor) {
               load(b_dst, &map_b, k0, nb);
+            } else if (p.b_chunked) {
+              if (CG == 2)
+                tma_load_4d_pair(b_dst, &map_b, full, 0, k0, nb >> 6, t.batch);
+              else
+                tma_load_4d(b_dst, &map_b, full, 0, k0, nb >> 6, t.batch);
             } else {
               for (int j = 0; j < b_rows / 64; ++j) load(b_dst + j * 8192, &map_b, nb + 64 * j, k0);
             }
@@ -815,21 +826,32 @@ int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* parti
   }
 
   CUtensorMap map_a, map_b;
-  bool ok;
+  bool ok, a_chunked = false, b_chunked = false;
   const bool a_blocked = d.a_layout == B200_LAYOUT_BLOCKED;
   if (a_blocked) {
     const int64_t mb = round_up(d.m, 32) / 32, kb = round_up(d.k, 32) / 32;
     ok = encode_map_blocked(&map_a, d.a, mb, kb, d.batch, d.batch > 1 ? d.stride_a : mb * kb * 1024, kBlockM / 32);
   } else if (a_kmajor)
     ok = encode_map(&map_a, d.a, d.k, d.m, d.batch, d.lda, d.batch > 1 ? d.stride_a : d.lda * d.m, kStageK, kBlockM);
-  else
-    ok = encode_map(&map_a, d.a, d.m, d.k, d.batch, d.lda, d.batch > 1 ? d.stride_a : d.lda * d.k, 64, kStageK);
+  else {
+    // [K, M]: with M in whole 64-column chunks both chunks of a stage arrive in one copy
+    a_chunked = d.m % 64 == 0 && encode_map_chunked(&map_a, d.a, d.m, d.k, d.batch, d.lda,
+                                                    d.batch > 1 ? d.stride_a : d.lda * d.k, kStageK, kBlockM / 64);
+    ok = a_chunked ||
+         encode_map(&map_a, d.a, d.m, d.k, d.batch, d.lda, d.batch > 1 ? d.stride_a : d.lda * d.k, 64, kStageK);
+  }
   if (!ok) return refuse(B200_E_DEVICE);
   if (b_kmajor)
     ok = encode_map(&map_b, d.b, d.k, d.n, d.batch, d.ldb, d.batch > 1 ? d.stride_b : d.ldb * d.n, kStageK,
                     plan.block_n / plan.cta_group);
-  else
-    ok = encode_map(&map_b, d.b, d.n, d.k, d.batch, d.ldb, d.batch > 1 ? d.stride_b : d.ldb * d.k, 64, kStageK);
+  else {
+    // [K, N]: the same for N
+    b_chunked = d.n % 64 == 0 &&
+                encode_map_chunked(&map_b, d.b, d.n, d.k, d.batch, d.ldb, d.batch > 1 ? d.stride_b : d.ldb * d.k, kStageK,
+                                   static_cast<uint32_t>(plan.block_n / plan.cta_group / 64));
+    ok = b_chunked ||
+         encode_map(&map_b, d.b, d.n, d.k, d.batch, d.ldb, d.batch > 1 ? d.stride_b : d.ldb * d.k, 64, kStageK);
+  }
   if (!ok) return refuse(B200_E_DEVICE);
 
   UmmaParams p{};
@@ -847,6 +869,8 @@ int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* parti
   p.stages = plan.stages;
   p.a_kmajor = a_kmajor;
   p.b_kmajor = b_kmajor;
+  p.a_chunked = a_chunked;
+  p.b_chunked = b_chunked;
   p.idesc = make_idesc(plan.block_n, a_kmajor, b_kmajor, plan.cta_group);
   p.a_stage_bytes = kBlockM * 128;
   p.b_stage_bytes = static_cast<uint32_t>(plan.block_n / plan.cta_group) * 128;  // this CTA's share of the B tile
