@@ -205,10 +205,13 @@ class FusedColumnShardedLinear:
         desc.a, desc.b, desc.bias = x.data_ptr(), weight_shard.data_ptr(), native.ptr(bias)
         desc.c = self.copies[buffer][self.rank] + self.n0 * item
         out = native.PeerOut()
-        out.count, out.rank, out.epoch = self.world, self.rank, self.epoch
-        for r in range(self.world):
-            out.c[r] = self.copies[buffer][r] + self.n0 * item
-            out.flags[r] = self.copies[buffer][r] + self.flag_offset + 4 * self.rank  # my word on rank r
+        out.count, out.rank, out.epoch = self.world, 0, self.epoch
+        # Destinations in rotated order, this rank's own copy first: at any moment the ranks
+        # store to different GPUs instead of all to the same one.
+        for slot in range(self.world):
+            r = (self.rank + slot) % self.world
+            out.c[slot] = self.copies[buffer][r] + self.n0 * item
+            out.flags[slot] = self.copies[buffer][r] + self.flag_offset + 4 * self.rank  # my word on rank r
         out.done_counter = self.local[buffer] + self.flag_offset + 256
         lib = native.module()
         stream = native.stream_ptr(self.device)
