@@ -364,7 +364,16 @@ extern "C" int b200_gemm_to_peers(const b200_gemm_desc* desc, const b200_peer_ou
     peers.flags[j] = out->flags[j];
   }
   peers.done_counter = out->done_counter;
+  peers.store_maps = out->store_maps;
+  if (out->store_maps && !aligned(out->store_maps, 64)) return refuse(B200_E_ALIGN);
   return run_gemm_umma(d, r.epi, nullptr, static_cast<cudaStream_t>(stream), &peers);
+}
+
+extern "C" int b200_peer_store_maps(void* device_maps, void* const* c, int32_t count, int64_t rows, int64_t cols,
+                                    int64_t ld) {
+  if (!enabled()) return refuse(B200_E_DISABLED);
+  if (device_info().sm_count == 0) return refuse(B200_E_DEVICE);
+  return store_peer_maps(device_maps, c, count, rows, cols, ld);
 }
 
 extern "C" int b200_peer_wait(const int32_t* flags, int32_t count, int32_t epoch, uint64_t budget_ns, void* stream) {

@@ -76,11 +76,13 @@ struct PeerOut {
   int64_t delta[8];        // byte offset from this GPU's C to copy j
   int32_t* flags[8];       // word on GPU j that this GPU's kernel sets to `epoch` when its stores are done
   uint32_t* done_counter;  // on this GPU: CTAs that have finished (reset by the last one)
+  const void* store_maps;  // on this GPU: `count` tensor maps, one per copy (NULL: plain stores)
 };
 
 int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* partials, cudaStream_t stream,
                   const PeerOut* peers = nullptr);
 int umma_supports(const b200_gemm_desc& d);
+int store_peer_maps(void* device_maps, void* const* c, int count, int64_t rows, int64_t cols, int64_t ld);
 int run_peer_wait(const int32_t* flags, int count, int32_t epoch, unsigned long long budget_ns, cudaStream_t stream);
 
 // One f32 operand to be widened into its six-fold bf16 split (split_f32_kernel, pack.cu).

@@ -482,18 +482,35 @@ __global__ void __launch_bounds__(kThreads, 1)
                   *reinterpret_cast<uint4*>(stage + lane * 128 + (((4 * h + j) ^ (lane & 7)) << 4)) = q;
                 }
               }
-              __syncwarp();
-              const int piece = lane & 7;
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const int r = 4 * i + (lane >> 3);
-                const uint4 q = *reinterpret_cast<const uint4*>(stage + r * 128 + ((piece ^ (r & 7)) << 4));
-                if (row0 + r < p.m) {
-                  uint8_t* to = c_tile + static_cast<int64_t>(r) * p.ldc * 2 + (static_cast<int64_t>(t.n0) + c0) * 2 + piece * 16;
-                  for (int dest = 0; dest < p.peer.count; ++dest) *reinterpret_cast<uint4*>(to + p.peer.delta[dest]) = q;
+              if (p.peer.store_maps) {
+                // The tile is laid out as TMA's 128-byte swizzle wants it: one bulk tensor store
+                // per copy of C moves the 32 x 64 box (rows past M are dropped), issued by one
+                // lane, instead of 64 store instructions of the whole warp. The stores read shared
+                // memory through the async proxy, hence the fence after the generic writes.
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) {
+                  const CUtensorMap* maps = static_cast<const CUtensorMap*>(p.peer.store_maps);
+                  for (int dest = 0; dest < p.peer.count; ++dest)
+                    tma_store_2d(maps + dest, smem_u32(stage), t.n0 + c0, static_cast<int32_t>(row0));
+                  tma_store_commit();
+                  tma_store_wait_read();  // the tile may be overwritten by the next 64 columns
                 }
+                __syncwarp();
+              } else {
+                __syncwarp();
+                const int piece = lane & 7;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const int r = 4 * i + (lane >> 3);
+                  const uint4 q = *reinterpret_cast<const uint4*>(stage + r * 128 + ((piece ^ (r & 7)) << 4));
+                  if (row0 + r < p.m) {
+                    uint8_t* to = c_tile + static_cast<int64_t>(r) * p.ldc * 2 + (static_cast<int64_t>(t.n0) + c0) * 2 + piece * 16;
+                    for (int dest = 0; dest < p.peer.count; ++dest) *reinterpret_cast<uint4*>(to + p.peer.delta[dest]) = q;
+                  }
+                }
+                __syncwarp();
               }
-              __syncwarp();
             }
             tc_fence_before();
             __syncwarp();
@@ -596,7 +613,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   // Neither CTA of a pair may leave while the other can still read its shared
   // memory (MMA operands) or signal its barriers.
   if constexpr (PEERS) {
-    if (warp < kEpilogueWarps) __threadfence_system();  // this thread's stores, before the CTA reports
+    if (warp < kEpilogueWarps) {
+      if (p.peer.store_maps && lane == 0) tma_store_wait_all();  // this lane's bulk stores have completed
+      __threadfence_system();  // this thread's stores, before the CTA reports
+    }
   }
   tc_fence_before();
   if (CG == 2)
@@ -966,6 +986,25 @@ int run_gemm_umma(const b200_gemm_desc& d, const GemmEpilogue& epi, float* parti
   if (rc != 0) return finish(rc);
   return launch_splitk_reduce(partials, plan.psplits, d.batch, d.m, d.n, d.c, d.out_dtype == B200_BF16, d.ldc,
                               d.stride_c, epi, stream);
+}
+
+// Encodes one store map per copy of C ([rows, cols] bf16, rows `ld` apart, boxes of 32 rows x
+// 64 columns) and writes them to `device_maps` (count x 128 bytes, 64-byte aligned) on the
+// current device. Synchronous: a set-up step.
+int store_peer_maps(void* device_maps, void* const* c, int count, int64_t rows, int64_t cols, int64_t ld) {
+  if (!device_maps || !c || count < 1 || count > B200_MAX_PEERS) return refuse(B200_E_ARG);
+  if (!aligned(device_maps, 64) || cols % 8 || ld % 8) return refuse(B200_E_ALIGN);
+  CUtensorMap maps[B200_MAX_PEERS];
+  for (int j = 0; j < count; ++j) {
+    if (!c[j] || !aligned(c[j], 16)) return refuse(B200_E_ALIGN);
+    if (!encode_store_map(&maps[j], c[j], cols, rows, ld, 32)) return refuse(B200_E_DEVICE);
+  }
+  const cudaError_t err = cudaMemcpy(device_maps, maps, sizeof(CUtensorMap) * count, cudaMemcpyHostToDevice);
+  if (err != cudaSuccess) {
+    cudaGetLastError();
+    return finish(-static_cast<int>(err));
+  }
+  return finish(0);
 }
 
 int run_peer_wait(const int32_t* flags, int count, int32_t epoch, unsigned long long budget_ns, cudaStream_t stream) {

@@ -124,6 +124,7 @@ class PeerOut(ctypes.Structure):
         ("c", c_void_p * MAX_PEERS),
         ("flags", c_void_p * MAX_PEERS),
         ("done_counter", c_void_p),
+        ("store_maps", c_void_p),
     ]
 
 
@@ -185,6 +186,7 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "b200_column_sum_static_fits": (c_int, [c_int64, c_int64, c_size_t]),
     "b200_eltwise": (c_int, [c_int32, c_int32, c_void_p, c_void_p, c_int64, c_float, c_void_p]),
     "b200_gemm_to_peers": (c_int, [ctypes.POINTER(GemmDesc), ctypes.POINTER(PeerOut), c_void_p]),
+    "b200_peer_store_maps": (c_int, [c_void_p, ctypes.POINTER(c_void_p), c_int32, c_int64, c_int64, c_int64]),
     "b200_peer_wait": (c_int, [c_void_p, c_int32, c_int32, c_uint64, c_void_p]),
     "b200_symm_alloc": (c_int, [c_size_t, ctypes.POINTER(c_void_p), c_void_p]),
     "b200_symm_open": (c_int, [c_void_p, ctypes.POINTER(c_void_p)]),

@@ -142,9 +142,10 @@ class FusedColumnShardedLinear:
         self.n0, self.n1 = shard_bounds(n, self.world, self.rank)
         lib = native.module()
         self.y_bytes = m * n * dtype.itemsize
-        # per buffer: the copy of y, then `world` flag words, then the CTA counter (256-byte slots)
+        # per buffer: the copy of y, then `world` flag words, the CTA counter (256-byte slots),
+        # and this rank's store descriptors for the copies (128 bytes each)
         self.flag_offset = -(-self.y_bytes // 256) * 256
-        self.block_bytes = self.flag_offset + 512
+        self.block_bytes = self.flag_offset + 512 + 128 * native.MAX_PEERS
         self.local: list[int] = []
         handles: list[bytes] = []
         with native.on_device(device):
@@ -172,6 +173,18 @@ class FusedColumnShardedLinear:
         self.results = [
             torch.as_tensor(_DeviceBlock(self.local[b], self.y_bytes), device=device).view(dtype).view(m, n) for b in range(2)
         ]
+        # Destinations in rotated order, this rank's own copy first: at any moment the ranks
+        # store to different GPUs instead of all to the same one. Where this rank's columns
+        # start in each copy, and the bulk-store descriptors for them, are fixed per buffer.
+        item = dtype.itemsize
+        self.order = [(self.rank + slot) % self.world for slot in range(self.world)]
+        self.targets = [[self.copies[b][r] + self.n0 * item for r in self.order] for b in range(2)]
+        self.store_maps = [self.local[b] + self.flag_offset + 512 for b in range(2)]
+        with native.on_device(device):
+            for b in range(2):
+                bases = (ctypes.c_void_p * self.world)(*self.targets[b])
+                native.check("b200_peer_store_maps", lib.b200_peer_store_maps(
+                    self.store_maps[b], bases, self.world, m, self.n1 - self.n0, n))
         self.epoch = 0
         self._plans: dict[object, object] = {}
         dist.barrier(group=group)  # every rank has mapped every copy before any store
@@ -203,15 +216,13 @@ class FusedColumnShardedLinear:
         item = self.dtype.itemsize
         desc = native.GemmDesc.from_buffer_copy(plan.desc)
         desc.a, desc.b, desc.bias = x.data_ptr(), weight_shard.data_ptr(), native.ptr(bias)
-        desc.c = self.copies[buffer][self.rank] + self.n0 * item
+        desc.c = self.targets[buffer][0]
         out = native.PeerOut()
         out.count, out.rank, out.epoch = self.world, 0, self.epoch
-        # Destinations in rotated order, this rank's own copy first: at any moment the ranks
-        # store to different GPUs instead of all to the same one.
-        for slot in range(self.world):
-            r = (self.rank + slot) % self.world
-            out.c[slot] = self.copies[buffer][r] + self.n0 * item
+        for slot, r in enumerate(self.order):
+            out.c[slot] = self.targets[buffer][slot]
             out.flags[slot] = self.copies[buffer][r] + self.flag_offset + 4 * self.rank  # my word on rank r
+        out.store_maps = self.store_maps[buffer]
         out.done_counter = self.local[buffer] + self.flag_offset + 256
         lib = native.module()
         stream = native.stream_ptr(self.device)

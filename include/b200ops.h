@@ -338,8 +338,15 @@ typedef struct b200_peer_out {
   void* c[B200_MAX_PEERS];         /* where C starts in copy j (device pointers valid on this GPU) */
   int32_t* flags[B200_MAX_PEERS];  /* the word on GPU j that this GPU raises */
   uint32_t* done_counter;          /* a zeroed word on this GPU, private to these calls */
+  const void* store_maps;          /* NULL, or what b200_peer_store_maps wrote for these c[]: the results then
+                                      leave as one bulk tensor store per copy and 32 x 64 piece */
 } b200_peer_out;
 int b200_gemm_to_peers(const b200_gemm_desc* desc, const b200_peer_out* out, void* stream);
+/* Set-up for bulk tensor stores: encodes one store descriptor per copy (c[j] = where this
+ * rank's columns start in copy j, `rows` x `cols` bf16 values, rows `ld` elements apart) and
+ * writes them to `device_maps` (count x 128 bytes of this GPU's memory, 64-byte aligned).
+ * Synchronous; call once per set of copies, then pass `device_maps` as store_maps. */
+int b200_peer_store_maps(void* device_maps, void* const* c, int32_t count, int64_t rows, int64_t cols, int64_t ld);
 /* Waits (on the device, `stream` order) until flags[0..count) have all reached `epoch`. */
 int b200_peer_wait(const int32_t* flags, int32_t count, int32_t epoch, uint64_t budget_ns, void* stream);
 int b200_symm_alloc(size_t bytes, void** out_ptr, void* out_handle /* B200_IPC_HANDLE_BYTES */);
