@@ -955,6 +955,8 @@ def run_block(key: str, harness: Harness, rank: int, with_cpu: bool) -> dict[str
     block: dict[str, object] = {
         "metric": workload.metric, "value": per_gpu * harness.world, "unit": workload.unit, "per_gpu": per_gpu,
         "ms_per_step": ms / repeats, "inner_repeats": repeats,
+        "burst": {"per_gpu": work * 10 / (pilot_ms * 1e-3) / scale, "steps": 10, "ms_per_step": pilot_ms / 10,
+                  "note": "the 10 pilot steps after 5 warm-up steps, before the power cap bites; `value` is the 300 ms run"},
         "timing": f"{repeats} steps back to back (sized for {BLOCK_TARGET_MS:.0f} ms of device time, independent of --steps), CUDA events, max over ranks",
         "dtype": workload.dtype, "config": workload.config(), "roofline": harness.roofline(workload, per_gpu),
         "gpu_launches": launches, "clocks": clocks,
