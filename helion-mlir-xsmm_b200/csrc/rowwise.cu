@@ -612,6 +612,10 @@ int launch_rowwise_lean(const RowParams& p, int cta_threads, cudaStream_t stream
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, cta_threads, 0) != cudaSuccess || per_sm < 1)
     per_sm = 1;
   const int64_t wanted = ceil_div(p.rows, rows_per_cta);
+  // Three resident CTAs per SM at most: each keeps a row in flight ahead of the one it
+  // reduces, and a fourth (the f32 softmax and rms_norm fit four) made the six kernels of
+  // [32768, 4096] 1.5 % slower together (6038 against 6131 GB/s; two: 5815, one: 4260).
+  if (per_sm > 3) per_sm = 3;
   const int64_t resident = static_cast<int64_t>(device_info().sm_count) * per_sm;
   kernel<<<static_cast<unsigned>(wanted < resident ? wanted : resident), cta_threads, 0, stream>>>(p);
   return launched();
