@@ -3,8 +3,9 @@
 // Bandwidth-bound kernels: every element of x is read from HBM once (one
 // 128-bit load where rows are 16-byte aligned), kept in registers while the row
 // statistics are reduced (warp shuffles, then shared memory across the warps of
-// a row), and written once. A row is owned by `tpr` threads (a power of two,
-// 32..1024); a CTA holds 256/tpr rows (at least one) and walks the rows with a
+// a row), and written once. A row is owned by `tpr` threads (a power of two from 4
+// up, or any number of whole warps that covers the row exactly, up to 512; 1024 in the
+// two-pass kernel); a CTA holds 256/tpr rows (at least one) and walks the rows with a
 // grid stride, so the grid is sized to the SM count times the resident CTAs.
 //
 // Arithmetic follows the bodies these kernels replace
@@ -44,6 +45,7 @@ __device__ __forceinline__ float load_param(const void* p, int64_t i, int bf16) 
 }
 
 constexpr int kMaxWarpsPerRow = 32;
+constexpr int64_t kRowBytesInFlight = 48 * 1024;  // per SM, for the kernels that load a row ahead
 
 // Reduces `v` over the `tpr` threads of a row. `scratch` has room for
 // rows_per_cta * warps_per_row floats. Every thread of the CTA must call this.
@@ -295,10 +297,15 @@ __device__ __forceinline__ void load_param_vec(const PT* p, float (&out)[EPV]) {
   }
 }
 
-template <typename T, typename PT, int VPT, int OP, int MAXT>
+// TAIL: n < tpr * VPT, so the last vectors of some threads lie beyond the row. They are
+// not loaded but filled with the neutral value of the reduction (-inf for the maximum,
+// whose exponential is 0; 0 for the sums), left out of the centred sum of squares, and
+// neither read their parameters nor are stored.
+template <typename T, typename PT, int VPT, int OP, int MAXT, bool TAIL>
 __global__ void __launch_bounds__(MAXT) rowwise_lean_kernel(const RowParams p) {
   constexpr int EPV = Elem<T>::kVec;
   constexpr int NV = VPT / EPV;
+  constexpr uint32_t kFillWord = OP != kSoftmax ? 0u : (sizeof(T) == 2 ? 0xff80ff80u : 0xff800000u);
   constexpr float kLog2e = 1.4426950408889634f;
   __shared__ float red_a[kMaxWarpsPerRow];
   __shared__ float red_b[kMaxWarpsPerRow];
@@ -316,6 +323,9 @@ __global__ void __launch_bounds__(MAXT) rowwise_lean_kernel(const RowParams p) {
   const PT* __restrict__ weight = reinterpret_cast<const PT*>(p.weight) + col0;
   const PT* __restrict__ bias = reinterpret_cast<const PT*>(p.bias) + col0;
   const float inv_n = 1.f / static_cast<float>(p.n);
+  const int n = static_cast<int>(p.n);
+  auto within = [&](int i) { return !TAIL || col0 + i * col_step < n; };
+  const uint4 fill = make_uint4(kFillWord, kFillWord, kFillWord, kFillWord);
 
   // The next row's loads are issued before this row's reductions, so that a CTA
   // always has a row in flight (twice the bytes in flight for NV more registers).
@@ -326,7 +336,7 @@ __global__ void __launch_bounds__(MAXT) rowwise_lean_kernel(const RowParams p) {
     const int64_t r0 = first + row_in_cta;
     const T* xr = x + (r0 < p.rows ? r0 : p.rows - 1) * p.ld;  // dead rows re-read a valid row, store nothing
 #pragma unroll
-    for (int i = 0; i < NV; ++i) raw[i] = ld_stream16(xr + i * col_step);
+    for (int i = 0; i < NV; ++i) raw[i] = within(i) ? ld_stream16(xr + i * col_step) : fill;
   }
   for (int64_t base = first; base < p.rows; base += row_stride) {
     const int64_t row = base + row_in_cta;
@@ -339,7 +349,7 @@ __global__ void __launch_bounds__(MAXT) rowwise_lean_kernel(const RowParams p) {
       const int64_t rn = row + row_stride;
       const T* xn = x + (rn < p.rows ? rn : p.rows - 1) * p.ld;
 #pragma unroll
-      for (int i = 0; i < NV; ++i) raw[i] = ld_stream16(xn + i * col_step);
+      for (int i = 0; i < NV; ++i) raw[i] = within(i) ? ld_stream16(xn + i * col_step) : fill;
     }
 
     if (OP == kSoftmax) {
@@ -396,7 +406,7 @@ __global__ void __launch_bounds__(MAXT) rowwise_lean_kernel(const RowParams p) {
 #pragma unroll
         for (int j = 0; j < EPV / 2; ++j) {
           pair[i][j] = add_f32x2(pair[i][j], neg_mean2);
-          q2 = fma_f32x2(pair[i][j], pair[i][j], q2);
+          if (within(i)) q2 = fma_f32x2(pair[i][j], pair[i][j], q2);
         }
       float q_lo, q_hi;
       unpack_f32x2(q2, q_lo, q_hi);
@@ -406,6 +416,7 @@ __global__ void __launch_bounds__(MAXT) rowwise_lean_kernel(const RowParams p) {
       const int chan0 = p.groups > 1 ? static_cast<int>(row_c % p.groups) * static_cast<int>(p.n) : 0;
 #pragma unroll
       for (int i = 0; i < NV; ++i) {
+        if (!within(i)) continue;
         float w[EPV], b[EPV];
         load_param_vec<EPV, PT>(weight + chan0 + i * col_step, w);
         load_param_vec<EPV, PT>(bias + chan0 + i * col_step, b);
@@ -432,6 +443,7 @@ __global__ void __launch_bounds__(MAXT) rowwise_lean_kernel(const RowParams p) {
       const uint64_t rstd2 = pack_f32x2(rstd, rstd);
 #pragma unroll
       for (int i = 0; i < NV; ++i) {
+        if (!within(i)) continue;
         float w[EPV];
         load_param_vec<EPV, PT>(weight + i * col_step, w);
 #pragma unroll
@@ -444,7 +456,8 @@ __global__ void __launch_bounds__(MAXT) rowwise_lean_kernel(const RowParams p) {
     if (live) {
       T* yr = y + row * p.ld;
 #pragma unroll
-      for (int i = 0; i < NV; ++i) st_stream16(yr + i * col_step, pack16(v[i]));
+      for (int i = 0; i < NV; ++i)
+        if (within(i)) st_stream16(yr + i * col_step, pack16(v[i]));
     }
   }
 }
@@ -604,26 +617,87 @@ int launch_rowwise_full(const RowParams& p, int cta_threads, cudaStream_t stream
   return launched();
 }
 
-template <typename T, typename PT, int VPT, int OP, int MAXT>
+template <typename T, typename PT, int VPT, int OP, int MAXT, bool TAIL>
 int launch_rowwise_lean(const RowParams& p, int cta_threads, cudaStream_t stream) {
   const int rows_per_cta = cta_threads / p.tpr;
   int per_sm = 0;
-  auto kernel = rowwise_lean_kernel<T, PT, VPT, OP, MAXT>;
+  auto kernel = rowwise_lean_kernel<T, PT, VPT, OP, MAXT, TAIL>;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, cta_threads, 0) != cudaSuccess || per_sm < 1)
     per_sm = 1;
   const int64_t wanted = ceil_div(p.rows, rows_per_cta);
-  // Three resident CTAs per SM at most: each keeps a row in flight ahead of the one it
-  // reduces, and a fourth (the f32 softmax and rms_norm fit four) made the six kernels of
-  // [32768, 4096] 1.5 % slower together (6038 against 6131 GB/s; two: 5815, one: 4260).
-  if (per_sm > 3) per_sm = 3;
+  // No more resident CTAs per SM than put kRowBytesInFlight of loads in flight (each thread
+  // keeps the next row's VPT values in flight while it reduces this row's). For the six
+  // kernels of [32768, 4096] that is three CTAs of 256 threads x 64 bytes; a fourth (the f32
+  // softmax and rms_norm fit four) made them 1.5 % slower together (6038 against 6131 GB/s;
+  // two CTAs: 5815, one: 4260).
+  const int64_t cta_bytes = static_cast<int64_t>(cta_threads) * VPT * sizeof(T);
+  const int enough = static_cast<int>(ceil_div(kRowBytesInFlight, cta_bytes));
+  if (per_sm > enough) per_sm = enough;
   const int64_t resident = static_cast<int64_t>(device_info().sm_count) * per_sm;
   kernel<<<static_cast<unsigned>(wanted < resident ? wanted : resident), cta_threads, 0, stream>>>(p);
   return launched();
 }
 
-// Whether the lean kernel applies: no masks, vector parameters, plain affine form.
+// Threads per row (whole warps) and values per thread for a row of `n` elements that no
+// power-of-two number of threads covers exactly (768, 5120, 11008, 12288 ...). An exact
+// cover (n == tpr * vpt) is looked for first, then one whose last vectors partly lie beyond
+// the row. Either way the lean kernel applies, where the masked kernel, which keeps no row in
+// flight ahead, ran at 1.3 to 3.4 TB/s (bf16, 10240 to 12288 columns). Values per thread are
+// tried in the order 64, 96 or 128, then 48 or 32, then 16 bytes of loads per thread; the
+// first whose resident CTAs (by an estimate of the registers) put 40 KB in flight is taken,
+// else the one with the most. {0, 0}: none (rows shorter than a warp's vectors). Measured
+// (TB/s, softmax / layer_norm / rms_norm, about 1 GB of rows), masked kernel -> this:
+// bf16 768: 4.8 / 2.5 / 3.7 -> 5.8 / 6.2 / 5.9; bf16 12288: 3.5 / 1.4 / 2.8 -> 6.2 / 5.9 / 6.4;
+// f32 5120: 6.2 / 3.1 / 4.2 -> 5.8 / 5.6 / 5.8; f32 11008 (a tail): 4.8 / 3.5 / 3.0 -> 5.3 / 5.0 / 6.1.
+// Values per thread of f32 rows are tried from 16: [32768, 4096] as 128 threads x 32 values
+// ran at 5.8 / 5.6 / 5.8 against 6.2 / 6.3 / 6.0 as 256 x 16.
+struct RowCover {
+  int tpr, vpt;
+};
+inline RowCover row_cover(int64_t n, int elem_bytes, bool wide_tail) {
+  const int epv = 16 / elem_bytes;
+  const int order_f32[4] = {16, 24, 32, 8}, order_bf16[5] = {32, 64, 24, 16, 8};
+  const int* order = elem_bytes == 2 ? order_bf16 : order_f32;
+  const int count = elem_bytes == 2 ? 5 : 4;
+  for (int tail = 0; tail < 2; ++tail) {
+    RowCover best{0, 0};
+    int64_t best_bytes = 0;
+    for (int k = 0; k < count; ++k) {
+      const int vpt = order[k];
+      int64_t tpr;
+      if (!tail) {
+        if (n % vpt) continue;
+        tpr = n / vpt;
+        if (tpr % 32) continue;
+      } else {
+        // 64 values with a tail fit 128 registers for softmax only: layer_norm spilt
+        // 432 bytes and ran [24385, 11008] bf16 at 2.2 TB/s (softmax: 5.8)
+        if (vpt == 64 && !wide_tail) continue;
+        tpr = ceil_div(ceil_div(n, static_cast<int64_t>(vpt)), int64_t(32)) * 32;
+        if (tpr * (vpt - epv) >= n) continue;  // no thread's last vector starts within the row: fewer values do
+      }
+      if (tpr > (vpt >= 32 ? 512 : 256)) continue;
+      const int64_t cta = tpr >= 256 ? tpr : tpr * (256 / tpr);
+      const int64_t regs = vpt == 8 ? 48 : vpt == 16 ? 66 : vpt == 24 ? (elem_bytes == 4 ? 100 : 64)
+                                                     : vpt == 32 ? (elem_bytes == 4 ? 128 : 104) : 128;
+      int64_t ctas = 65536 / (regs * cta);
+      if (ctas > 2048 / cta) ctas = 2048 / cta;
+      if (ctas < 1) ctas = 1;
+      const int64_t bytes = ctas * (cta / tpr) * n * elem_bytes;  // the rows that the resident CTAs hold
+      if (bytes >= 40 * 1024) return RowCover{static_cast<int>(tpr), vpt};
+      if (bytes > best_bytes) {
+        best_bytes = bytes;
+        best = RowCover{static_cast<int>(tpr), vpt};
+      }
+    }
+    if (best.tpr) return best;
+  }
+  return RowCover{0, 0};
+}
+
+// Whether the lean kernel applies: whole vectors, vector parameters, plain affine form.
 inline bool lean_case(const RowParams& p, int op, int vpt, int epv) {
-  if (p.n != static_cast<int64_t>(p.tpr) * vpt || vpt % epv) return false;
+  if (p.n > static_cast<int64_t>(p.tpr) * vpt || vpt % epv) return false;
   if (op == kSoftmax) return true;
   if (!p.param_vec || p.extra_op != B200_NORM_EXTRA_NONE || p.act != B200_ACT_IDENTITY || !p.weight) return false;
   if (op == kGroupNorm) return p.bias != nullptr && p.groups * p.n < (int64_t(1) << 30);
@@ -634,8 +708,12 @@ template <typename T, bool VEC, int VPT, int OP, int MAXT>
 int launch_rowwise(const RowParams& p, int cta_threads, cudaStream_t stream) {
   if constexpr (VEC) {
     if (lean_case(p, OP, VPT, Elem<T>::kVec)) {
-      if (p.param_bf16) return launch_rowwise_lean<T, __nv_bfloat16, VPT, OP, MAXT>(p, cta_threads, stream);
-      return launch_rowwise_lean<T, float, VPT, OP, MAXT>(p, cta_threads, stream);
+      if (p.n == static_cast<int64_t>(p.tpr) * VPT) {
+        if (p.param_bf16) return launch_rowwise_lean<T, __nv_bfloat16, VPT, OP, MAXT, false>(p, cta_threads, stream);
+        return launch_rowwise_lean<T, float, VPT, OP, MAXT, false>(p, cta_threads, stream);
+      }
+      if (p.param_bf16) return launch_rowwise_lean<T, __nv_bfloat16, VPT, OP, MAXT, true>(p, cta_threads, stream);
+      return launch_rowwise_lean<T, float, VPT, OP, MAXT, true>(p, cta_threads, stream);
     }
   }
   return launch_rowwise_full<T, VEC, VPT, OP, MAXT, false>(p, cta_threads, stream);
@@ -648,6 +726,8 @@ int dispatch_vpt(const RowParams& p, int vpt, int cta_threads, cudaStream_t stre
       return launch_rowwise<T, VEC, 8, OP, 256>(p, cta_threads, stream);
     case 16:
       return launch_rowwise<T, VEC, 16, OP, 256>(p, cta_threads, stream);
+    case 24:  // three (bf16) or six (f32) vectors: rows of 768, 1536, 3072 ... elements
+      return launch_rowwise<T, VEC, 24, OP, 256>(p, cta_threads, stream);
     case 64:  // bf16 rows only: 64 f32 values beside their 16-byte loads do not fit 128 registers
       if constexpr (sizeof(T) == 2) return launch_rowwise<T, VEC, 64, OP, 512>(p, cta_threads, stream);
       return refuse(B200_E_SHAPE);
@@ -693,10 +773,22 @@ int run_rowwise(RowParams p, cudaStream_t stream) {
       rowwise_long_kernel<T, OP, false><<<grid, 1024, 0, stream>>>(p);
     return launched();
   }
-  const int vpt = vpt_needed <= 8 ? 8 : (vpt_needed <= 16 ? 16 : (vpt_needed <= 32 ? 32 : 64));
+  int vpt = vpt_needed <= 8 ? 8 : (vpt_needed <= 16 ? 16 : (vpt_needed <= 32 ? 32 : 64));
+  int cta_threads = tpr > 256 ? tpr : 256;
+  // The power-of-two cover above is kept where it is exact, but for bf16 rows of 512 threads
+  // x 32 values: one such CTA fits an SM and keeps 32 KB in flight (layer_norm of
+  // [8192, 16384]: 4.45 TB/s), two CTAs of 256 x 64 keep 64 KB (5.84 TB/s).
+  const bool exact = p.n == static_cast<int64_t>(tpr) * vpt;
+  if (vec && tpr >= 32 && (!exact || (sizeof(T) == 2 && tpr == 512 && vpt == 32))) {
+    const RowCover cover = row_cover(p.n, sizeof(T), OP == kSoftmax);
+    if (cover.tpr) {
+      tpr = cover.tpr;
+      vpt = cover.vpt;
+      cta_threads = tpr >= 256 ? tpr : tpr * (256 / tpr);
+    }
+  }
   p.tpr = tpr;
   p.param_vec = vec && aligned(p.weight, 16) && aligned(p.bias, 16) && aligned(p.extra, 16);
-  const int cta_threads = tpr > 256 ? tpr : 256;
   if (vec) return dispatch_vpt<T, true, OP>(p, vpt, cta_threads, stream);
   return dispatch_vpt<T, false, OP>(p, vpt, cta_threads, stream);
 }

@@ -108,6 +108,35 @@ def test_rms_norm(ops, shape, dtype) -> None:
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("n", [768, 1000, 1536, 2560, 3072, 5120, 6144, 10240, 11008, 12288, 14336, 16384, 20000])
+def test_row_lengths_that_whole_warps_cover(ops, n, dtype) -> None:
+    """Row lengths that no power-of-two number of threads covers run with a number of whole
+    warps per row that does (32 threads x 24 values for 768, 192 x 64 for bf16 12288 ...);
+    1000, 11008 and 20000 have no such cover: the last vectors of some threads lie beyond
+    the row and are filled, not loaded. More rows than one wave of CTAs holds, a row
+    count that leaves the last CTA of two-row CTAs half empty, and the grouped form whose
+    parameters depend on the row."""
+    rows = 1481
+    gen = torch.Generator().manual_seed(n)
+    x = (torch.randn(rows, n, generator=gen) * 2 + 0.25).to(dtype)
+    w = (1 + 0.1 * torch.randn(n, generator=gen)).to(dtype)
+    b = (0.1 * torch.randn(n, generator=gen)).to(dtype)
+    dx, dw, db = cuda(x, w, b)
+    bound = 2e-6 if dtype == F32 else 1e-2
+    assert checks.max_norm_rel(ops.softmax(dx).cpu(), ref.softmax(x)) < tol(dtype)
+    assert checks.max_norm_rel(ops.layer_norm(dx, dw, db, 1e-5).cpu(), ref.layer_norm(x, w, b, 1e-5)) < bound
+    assert checks.max_norm_rel(ops.rms_norm(dx, dw, 1e-5).cpu(), ref.rms_norm(x, w, 1e-5)) < bound
+    groups = 4
+    xg = x[:, : n // groups * groups].reshape(rows, -1)[:37]
+    wg, bg = w[: xg.shape[1]], b[: xg.shape[1]]
+    out = ops.group_norm(cuda(xg), groups, cuda(wg), cuda(bg), 1e-5)
+    assert checks.max_norm_rel(out.cpu(), ref.group_norm(xg, groups, wg, bg, 1e-5)) < bound
+    # an activation after the norm takes the masked kernel with the same threads per row
+    out = ops.group_norm(cuda(xg), groups, cuda(wg), cuda(bg), 1e-5, torch.relu)
+    assert checks.max_norm_rel(out.cpu(), torch.relu(ref.group_norm(xg, groups, wg, bg, 1e-5))) < bound
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
 def test_c4_configuration(ops, dtype) -> None:
     """x [rows, 4096] ~N(0,2) with 1% of entries at +-30; softmax, layer_norm, rms_norm and the chain."""
     data = inputs.c4_rows(m=512, n=4096, dtype=dtype)
