@@ -137,6 +137,44 @@ def test_row_lengths_that_whole_warps_cover(ops, n, dtype) -> None:
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("shape", [(700, 50304), (301, 32768), (150, 128256), (75, 131072), (300, 65536), (200, 40000),
+                                   (40, 262144), (9, 300000)])
+def test_rows_longer_than_registers_hold(ops, shape, dtype) -> None:
+    """Rows of more values than one CTA's registers hold (16 Ki f32, 32 Ki bf16) take the
+    two-pass kernel, one CTA per row: more rows than resident CTAs (so that every CTA walks
+    several rows), row lengths of vocabulary sizes, rows with NaN and infinities, in place,
+    and the grouped form."""
+    rows, n = shape
+    gen = torch.Generator().manual_seed(rows + n)
+    x = (torch.randn(rows, n, generator=gen) * 2 + 0.25).to(dtype)
+    w = (1 + 0.1 * torch.randn(n, generator=gen)).to(dtype)
+    b = (0.1 * torch.randn(n, generator=gen)).to(dtype)
+    dx, dw, db = cuda(x, w, b)
+    bound = 2e-6 if dtype == F32 else 1e-2
+    soft = ops.softmax(dx)
+    assert checks.max_norm_rel(soft.cpu(), ref.softmax(x)) < tol(dtype)
+    assert torch.equal(ops.softmax(dx), soft)  # fixed order over the warps
+    assert checks.max_norm_rel(ops.layer_norm(dx, dw, db, 1e-5).cpu(), ref.layer_norm(x, w, b, 1e-5)) < bound
+    assert checks.max_norm_rel(ops.rms_norm(dx, dw, 1e-5).cpu(), ref.rms_norm(x, w, 1e-5)) < bound
+    y = dx.clone()
+    assert torch.equal(ops.softmax(y, in_place=True), soft)
+    special = x[:6].clone().float()
+    special[0, n - 3] = float("nan")
+    special[1, 7] = float("inf")
+    special[2, :] = float("-inf")
+    special[3, n // 2] = float("-inf")
+    special[4, :] = 1e30
+    special = special.to(dtype)
+    out, expect = ops.softmax(cuda(special)).cpu().float(), torch.softmax(special.float(), -1)
+    assert torch.equal(out.isnan(), expect.isnan())
+    keep = ~expect.isnan()
+    assert (out[keep] - expect[keep]).abs().max() < (1e-6 if dtype == F32 else 1e-2)
+    groups = 2  # the grouped form: rows of n / 2 values whose parameters depend on the row
+    out = ops.group_norm(dx[:33], groups, dw, db, 1e-5)
+    assert checks.max_norm_rel(out.cpu(), ref.group_norm(x[:33], groups, w, b, 1e-5)) < bound
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
 def test_c4_configuration(ops, dtype) -> None:
     """x [rows, 4096] ~N(0,2) with 1% of entries at +-30; softmax, layer_norm, rms_norm and the chain."""
     data = inputs.c4_rows(m=512, n=4096, dtype=dtype)
