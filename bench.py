@@ -622,6 +622,13 @@ class BandwidthKernels(Workload):
         long32 = torch.randn(2048, 65536, generator=gen, device=device)
         sq16 = torch.randn(8192, 8192, generator=gen, device=device).bfloat16()
         sq32 = torch.randn(8192, 8192, generator=gen, device=device)
+        # rows that no power-of-two number of threads covers: 12288 = 192 threads x 64 values,
+        # 768 = 32 x 24, 11008 has only a cover with a tail
+        r12k = torch.randn(16384, 12288, generator=gen, device=device).bfloat16()
+        g12k, b12k = torch.randn(12288, device=device).bfloat16(), torch.randn(12288, device=device).bfloat16()
+        r768 = torch.randn(262144, 768, generator=gen, device=device).bfloat16()
+        g768, b768 = torch.randn(768, device=device).bfloat16(), torch.randn(768, device=device).bfloat16()
+        r11k = torch.randn(12288, 11008, generator=gen, device=device)
         f4, f2 = 4.0 * m * n, 2.0 * m * n
         t4, t2 = 4.0 * (1 << 20) * 64, 2.0 * (1 << 20) * 64
         s2, s4 = 2.0 * 8192 * 8192, 4.0 * 8192 * 8192
@@ -642,6 +649,9 @@ class BandwidthKernels(Workload):
             ("leaky_relu_bf16_32768x4096", 2 * f2, lambda: ops.leaky_relu(x16)),
             ("scalar_mul_f32_32768x4096", 2 * f4, lambda: ops.scalar_mul(x32, 1.5)),
             ("softmax_long_rows_f32_2048x65536", 2 * 4.0 * 2048 * 65536, lambda: ops.softmax(long32)),
+            ("layer_norm_bf16_16384x12288", 2 * 2.0 * 16384 * 12288, lambda: ops.layer_norm(r12k, g12k, b12k, 1e-5)),
+            ("layer_norm_bf16_262144x768", 2 * 2.0 * 262144 * 768, lambda: ops.layer_norm(r768, g768, b768, 1e-5)),
+            ("softmax_f32_12288x11008", 2 * 4.0 * 12288 * 11008, lambda: ops.softmax(r11k)),
             ("pack_a_blocked_bf16_8192", 2 * s2, lambda: ops.pack_a_blocked(sq16)),
             ("pack_a_blocked_t_bf16_8192", 2 * s2, lambda: ops.pack_a_blocked_t(sq16)),
             ("pack_b_blocked_vnni_bf16_8192", 2 * s2, lambda: ops.pack_b_blocked_vnni(sq16)),
