@@ -307,6 +307,9 @@ __global__ void __launch_bounds__(MAXT) rowwise_lean_kernel(const RowParams p) {
   constexpr int NV = VPT / EPV;
   constexpr uint32_t kFillWord = OP != kSoftmax ? 0u : (sizeof(T) == 2 ? 0xff80ff80u : 0xff800000u);
   constexpr float kLog2e = 1.4426950408889634f;
+  // bf16 norms of 56 or 64 values per thread with a tail: held as f32 beside the next row's
+  // loads they spill (216 to 432 bytes per thread; layer_norm of [8388, 32000] ran at 2.3 TB/s)
+  constexpr bool LAZY = TAIL && sizeof(T) == 2 && VPT >= 56 && OP != kSoftmax;
   __shared__ float red_a[kMaxWarpsPerRow];
   __shared__ float red_b[kMaxWarpsPerRow];
   const int tpr = p.tpr;
@@ -343,8 +346,14 @@ __global__ void __launch_bounds__(MAXT) rowwise_lean_kernel(const RowParams p) {
     const bool live = row < p.rows;
     const int64_t row_c = live ? row : p.rows - 1;
     float v[NV][EPV];
+    uint4 held[LAZY ? NV : 1];
+    if constexpr (LAZY) {
 #pragma unroll
-    for (int i = 0; i < NV; ++i) unpack16(raw[i], v[i]);
+      for (int i = 0; i < NV; ++i) held[i] = raw[i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) unpack16(raw[i], v[i]);
+    }
     if (base + row_stride < p.rows) {
       const int64_t rn = row + row_stride;
       const T* xn = x + (rn < p.rows ? rn : p.rows - 1) * p.ld;
@@ -381,6 +390,70 @@ __global__ void __launch_bounds__(MAXT) rowwise_lean_kernel(const RowParams p) {
       for (int i = 0; i < NV; ++i)
 #pragma unroll
         for (int j = 0; j < EPV / 2; ++j) unpack_f32x2(mul_f32x2(pair[i][j], inv2), v[i][2 * j], v[i][2 * j + 1]);
+    } else if (LAZY) {
+      // The row stays in its 16-bit form (half the registers) and is widened again in each of
+      // the passes; the operations per value and their order are those of the branches below.
+      auto widen = [&](int i, uint64_t (&out)[EPV / 2]) {
+        float f[EPV];
+        unpack16(held[i], f);
+#pragma unroll
+        for (int j = 0; j < EPV / 2; ++j) out[j] = pack_f32x2(f[2 * j], f[2 * j + 1]);
+      };
+      uint64_t centre2 = 0;  // (-mean, -mean) for group_norm, (0, 0) for rms_norm
+      if (OP == kGroupNorm) {
+        uint64_t s2 = 0;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+          uint64_t w2[EPV / 2];
+          widen(i, w2);
+#pragma unroll
+          for (int j = 0; j < EPV / 2; ++j) s2 = add_f32x2(s2, w2[j]);
+        }
+        float s_lo, s_hi;
+        unpack_f32x2(s2, s_lo, s_hi);
+        const float s = row_reduce<false>(s_lo + s_hi, red_a, warps_per_row, row_in_cta, warp_in_row, lane, width);
+        const float mean = s * inv_n;
+        centre2 = pack_f32x2(-mean, -mean);
+      }
+      uint64_t q2 = 0;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        if (!within(i)) continue;
+        uint64_t w2[EPV / 2];
+        widen(i, w2);
+#pragma unroll
+        for (int j = 0; j < EPV / 2; ++j) {
+          const uint64_t d = OP == kGroupNorm ? add_f32x2(w2[j], centre2) : w2[j];
+          q2 = fma_f32x2(d, d, q2);
+        }
+      }
+      float q_lo, q_hi;
+      unpack_f32x2(q2, q_lo, q_hi);
+      const float q = row_reduce<false>(q_lo + q_hi, OP == kGroupNorm ? red_b : red_a, warps_per_row, row_in_cta,
+                                        warp_in_row, lane, width);
+      const float rstd = rsqrtf(q * inv_n + p.eps);
+      const uint64_t rstd2 = pack_f32x2(rstd, rstd);
+      const int chan0 = OP == kGroupNorm && p.groups > 1 ? static_cast<int>(row_c % p.groups) * static_cast<int>(p.n) : 0;
+      T* yr = y + row * p.ld;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        if (!within(i)) continue;
+        uint64_t w2[EPV / 2];
+        widen(i, w2);
+        float w[EPV], b[EPV], out[EPV];
+        load_param_vec<EPV, PT>(weight + chan0 + i * col_step, w);
+        if (OP == kGroupNorm) load_param_vec<EPV, PT>(bias + chan0 + i * col_step, b);
+#pragma unroll
+        for (int j = 0; j < EPV / 2; ++j) {
+          const uint64_t d = OP == kGroupNorm ? add_f32x2(w2[j], centre2) : w2[j];
+          const uint64_t scaled = mul_f32x2(d, rstd2), gain = pack_f32x2(w[2 * j], w[2 * j + 1]);
+          w2[j] = OP == kGroupNorm ? fma_f32x2(scaled, gain, pack_f32x2(b[2 * j], b[2 * j + 1])) : mul_f32x2(scaled, gain);
+        }
+#pragma unroll
+        for (int j = 0; j < EPV / 2; ++j) unpack_f32x2(w2[j], out[2 * j], out[2 * j + 1]);
+        if (live) st_stream16(yr + i * col_step, pack16(out));
+      }
+      if (OP == kRmsNorm && warps_per_row > 1) __syncthreads();  // same two-barrier cadence as the other ops
     } else if (OP == kGroupNorm) {
       // The arithmetic runs on pairs (packed f32x2 instructions: one issue slot for two
       // values; the bf16 kernels are bound by instruction issue, not by HBM). Per value
@@ -453,7 +526,7 @@ __global__ void __launch_bounds__(MAXT) rowwise_lean_kernel(const RowParams p) {
       }
       if (warps_per_row > 1) __syncthreads();  // same two-barrier cadence as the other ops
     }
-    if (live) {
+    if (live && !LAZY) {
       T* yr = y + row * p.ld;
 #pragma unroll
       for (int i = 0; i < NV; ++i)
@@ -728,6 +801,15 @@ int dispatch_vpt(const RowParams& p, int vpt, int cta_threads, cudaStream_t stre
       return launch_rowwise<T, VEC, 16, OP, 256>(p, cta_threads, stream);
     case 24:  // three (bf16) or six (f32) vectors: rows of 768, 1536, 3072 ... elements
       return launch_rowwise<T, VEC, 24, OP, 256>(p, cta_threads, stream);
+    case 40:  // bf16 rows of 512 threads whose length is no multiple of 512 x 64: the fewest
+    case 48:  // vectors per thread that cover the row (64 values with a tail spill in the norms:
+    case 56:  // layer_norm of [13421, 20000] ran at 1.6 TB/s)
+      if constexpr (sizeof(T) == 2 && VEC) {
+        if (vpt == 40) return launch_rowwise<T, VEC, 40, OP, 512>(p, cta_threads, stream);
+        if (vpt == 48) return launch_rowwise<T, VEC, 48, OP, 512>(p, cta_threads, stream);
+        return launch_rowwise<T, VEC, 56, OP, 512>(p, cta_threads, stream);
+      }
+      [[fallthrough]];
     case 64:  // bf16 rows only: 64 f32 values beside their 16-byte loads do not fit 128 registers
       if constexpr (sizeof(T) == 2) return launch_rowwise<T, VEC, 64, OP, 512>(p, cta_threads, stream);
       return refuse(B200_E_SHAPE);
@@ -774,6 +856,7 @@ int run_rowwise(RowParams p, cudaStream_t stream) {
     return launched();
   }
   int vpt = vpt_needed <= 8 ? 8 : (vpt_needed <= 16 ? 16 : (vpt_needed <= 32 ? 32 : 64));
+  if (sizeof(T) == 2 && vec && vpt == 64) vpt = static_cast<int>(round_up(vpt_needed, 8));  // 40, 48, 56 or 64
   int cta_threads = tpr > 256 ? tpr : 256;
   // The power-of-two cover above is kept where it is exact, but for bf16 rows of 512 threads
   // x 32 values: one such CTA fits an SM and keeps 32 KB in flight (layer_norm of

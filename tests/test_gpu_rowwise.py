@@ -108,12 +108,15 @@ def test_rms_norm(ops, shape, dtype) -> None:
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
-@pytest.mark.parametrize("n", [768, 1000, 1536, 2560, 3072, 5120, 6144, 10240, 11008, 12288, 14336, 16384, 20000])
+@pytest.mark.parametrize("n", [768, 1000, 1536, 2560, 3072, 5120, 6144, 10240, 11008, 12288, 14336, 16384, 17000, 20000,
+                               24000, 25600, 30000, 32000])
 def test_row_lengths_that_whole_warps_cover(ops, n, dtype) -> None:
     """Row lengths that no power-of-two number of threads covers run with a number of whole
     warps per row that does (32 threads x 24 values for 768, 192 x 64 for bf16 12288 ...);
     1000, 11008 and 20000 have no such cover: the last vectors of some threads lie beyond
-    the row and are filled, not loaded. More rows than one wave of CTAs holds, a row
+    the row and are filled, not loaded. bf16 rows beyond 16384 values take 512 threads x 40,
+    48, 56 or 64 values; with a tail the norms of 56 and 64 keep the row in its 16-bit form
+    and widen it again in every pass. More rows than one wave of CTAs holds, a row
     count that leaves the last CTA of two-row CTAs half empty, and the grouped form whose
     parameters depend on the row."""
     rows = 1481
