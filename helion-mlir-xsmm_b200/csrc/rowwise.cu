@@ -540,6 +540,154 @@ __global__ void __launch_bounds__(MAXT) rowwise_lean_kernel(const RowParams p) {
   }
 }
 
+// Sums `v[0..R)` over the threads of a row group, as row_reduce does for one value: every
+// thread of the group gets the same bits. `scratch` holds R floats per warp of the CTA.
+template <int R>
+__device__ __forceinline__ void row_reduce_sums(float (&v)[R], float* scratch, int warps_per_row, int group,
+                                                int warp_in_row, int lane, int width) {
+  for (int o = width >> 1; o > 0; o >>= 1) {
+#pragma unroll
+    for (int k = 0; k < R; ++k) v[k] += __shfl_xor_sync(0xffffffffu, v[k], o);
+  }
+  if (warps_per_row <= 1) return;
+  if (lane == 0) {
+#pragma unroll
+    for (int k = 0; k < R; ++k) scratch[(group * warps_per_row + warp_in_row) * R + k] = v[k];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < R; ++k) {
+    float r = scratch[group * warps_per_row * R + k];
+    for (int w = 1; w < warps_per_row; ++w) r += scratch[(group * warps_per_row + w) * R + k];
+    v[k] = r;
+  }
+}
+
+// LayerNorm / RMSNorm of bf16 rows, two consecutive rows per group of `tpr` threads: a thread
+// holds the same columns of both rows, so the parameters of those columns are loaded and
+// widened once for the two (with f32 parameters the one-row form is bound by L1 bandwidth:
+// four bytes of weight and bias per byte of x). Per value the
+// operations and their order are those of rowwise_lean_kernel. Whole vectors, vector
+// parameters, weight (and bias) present, one parameter set for all rows (groups == 1).
+template <typename T, typename PT, int VPT, int OP, bool TAIL>
+__global__ void __launch_bounds__(256) rowwise_pair_kernel(const RowParams p) {
+  static_assert(OP != kSoftmax, "the norms only");
+  constexpr int EPV = Elem<T>::kVec;
+  constexpr int NV = VPT / EPV;
+  constexpr int R = 2;
+  __shared__ float red_a[8 * R];
+  __shared__ float red_b[8 * R];
+  const int tpr = p.tpr;
+  const int groups_per_cta = blockDim.x / tpr;
+  const int group = threadIdx.x / tpr;
+  const int t = threadIdx.x - group * tpr;
+  const int lane = threadIdx.x & 31;
+  const int warps_per_row = tpr >> 5;
+  const int width = tpr < 32 ? tpr : 32;
+  const int warp_in_row = t >> 5;
+  const int col0 = t * EPV, col_step = tpr * EPV;
+  const T* __restrict__ x = reinterpret_cast<const T*>(p.x) + col0;
+  T* __restrict__ y = reinterpret_cast<T*>(p.y) + col0;
+  const PT* __restrict__ weight = reinterpret_cast<const PT*>(p.weight) + col0;
+  const PT* __restrict__ bias = reinterpret_cast<const PT*>(p.bias) + col0;
+  const float inv_n = 1.f / static_cast<float>(p.n);
+  const int n = static_cast<int>(p.n);
+  auto within = [&](int i) { return !TAIL || col0 + i * col_step < n; };
+  const uint4 zeros = make_uint4(0u, 0u, 0u, 0u);
+  const int64_t rows_per_cta = static_cast<int64_t>(groups_per_cta) * R;
+  const int64_t row_stride = static_cast<int64_t>(gridDim.x) * rows_per_cta;
+  const int64_t first = static_cast<int64_t>(blockIdx.x) * rows_per_cta;
+  uint4 raw[R][NV];
+  auto fetch = [&](int64_t base) {  // rows past the end re-read the last row, store nothing
+#pragma unroll
+    for (int k = 0; k < R; ++k) {
+      const int64_t r = base + group * R + k;
+      const T* xr = x + (r < p.rows ? r : p.rows - 1) * p.ld;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) raw[k][i] = within(i) ? ld_stream16(xr + i * col_step) : zeros;
+    }
+  };
+  fetch(first);
+  for (int64_t base = first; base < p.rows; base += row_stride) {
+    const int64_t row0 = base + group * R;
+    uint64_t pair[R][NV][EPV / 2];
+#pragma unroll
+    for (int k = 0; k < R; ++k)
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        float f[EPV];
+        unpack16(raw[k][i], f);
+#pragma unroll
+        for (int j = 0; j < EPV / 2; ++j) pair[k][i][j] = pack_f32x2(f[2 * j], f[2 * j + 1]);
+      }
+    if (base + row_stride < p.rows) fetch(base + row_stride);
+
+    if (OP == kGroupNorm) {
+      float s[R];
+#pragma unroll
+      for (int k = 0; k < R; ++k) {
+        uint64_t s2 = 0;
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+#pragma unroll
+          for (int j = 0; j < EPV / 2; ++j) s2 = add_f32x2(s2, pair[k][i][j]);
+        float lo, hi;
+        unpack_f32x2(s2, lo, hi);
+        s[k] = lo + hi;
+      }
+      row_reduce_sums<R>(s, red_a, warps_per_row, group, warp_in_row, lane, width);
+#pragma unroll
+      for (int k = 0; k < R; ++k) {
+        const float mean = s[k] * inv_n;
+        const uint64_t neg_mean2 = pack_f32x2(-mean, -mean);
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+#pragma unroll
+          for (int j = 0; j < EPV / 2; ++j) pair[k][i][j] = add_f32x2(pair[k][i][j], neg_mean2);
+      }
+    }
+    float q[R];
+#pragma unroll
+    for (int k = 0; k < R; ++k) {
+      uint64_t q2 = 0;
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int j = 0; j < EPV / 2; ++j)
+          if (within(i)) q2 = fma_f32x2(pair[k][i][j], pair[k][i][j], q2);
+      float lo, hi;
+      unpack_f32x2(q2, lo, hi);
+      q[k] = lo + hi;
+    }
+    row_reduce_sums<R>(q, OP == kGroupNorm ? red_b : red_a, warps_per_row, group, warp_in_row, lane, width);
+    uint64_t rstd2[R];
+#pragma unroll
+    for (int k = 0; k < R; ++k) {
+      const float rstd = rsqrtf(q[k] * inv_n + p.eps);
+      rstd2[k] = pack_f32x2(rstd, rstd);
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      if (!within(i)) continue;
+      float w[EPV], b[EPV];
+      load_param_vec<EPV, PT>(weight + i * col_step, w);
+      if (OP == kGroupNorm) load_param_vec<EPV, PT>(bias + i * col_step, b);
+#pragma unroll
+      for (int k = 0; k < R; ++k) {
+        float out[EPV];
+#pragma unroll
+        for (int j = 0; j < EPV / 2; ++j) {
+          const uint64_t scaled = mul_f32x2(pair[k][i][j], rstd2[k]), gain = pack_f32x2(w[2 * j], w[2 * j + 1]);
+          unpack_f32x2(OP == kGroupNorm ? fma_f32x2(scaled, gain, pack_f32x2(b[2 * j], b[2 * j + 1])) : mul_f32x2(scaled, gain),
+                       out[2 * j], out[2 * j + 1]);
+        }
+        if (row0 + k < p.rows) st_stream16(y + (row0 + k) * p.ld + i * col_step, pack16(out));
+      }
+    }
+    if (OP == kRmsNorm && warps_per_row > 1) __syncthreads();  // two barriers per row pair, as the other op
+  }
+}
+
 // Rows too long for registers: one CTA of 1024 threads per row, two passes over the
 // row for softmax and RMSNorm, three for GroupNorm (mean, centred variance, output);
 // the later passes hit L2 for rows up to tens of MB. VEC: 16-byte accesses.
@@ -733,6 +881,22 @@ int launch_rowwise_lean(const RowParams& p, int cta_threads, cudaStream_t stream
   return launched();
 }
 
+template <typename T, typename PT, int VPT, int OP, bool TAIL>
+int launch_rowwise_pair(const RowParams& p, int cta_threads, cudaStream_t stream) {
+  const int64_t rows_per_cta = static_cast<int64_t>(cta_threads / p.tpr) * 2;
+  int per_sm = 0;
+  auto kernel = rowwise_pair_kernel<T, PT, VPT, OP, TAIL>;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, cta_threads, 0) != cudaSuccess || per_sm < 1)
+    per_sm = 1;
+  const int64_t cta_bytes = static_cast<int64_t>(cta_threads) * VPT * 2 * sizeof(T);
+  const int enough = static_cast<int>(ceil_div(kRowBytesInFlight, cta_bytes));
+  if (per_sm > enough) per_sm = enough;
+  const int64_t wanted = ceil_div(p.rows, rows_per_cta);
+  const int64_t resident = static_cast<int64_t>(device_info().sm_count) * per_sm;
+  kernel<<<static_cast<unsigned>(wanted < resident ? wanted : resident), cta_threads, 0, stream>>>(p);
+  return launched();
+}
+
 // Threads per row (whole warps) and values per thread for a row of `n` elements that no
 // power-of-two number of threads covers exactly (768, 5120, 11008, 12288 ...). An exact
 // cover (n == tpr * vpt) is looked for first, then one whose last vectors partly lie beyond
@@ -802,6 +966,19 @@ inline bool lean_case(const RowParams& p, int op, int vpt, int epv) {
 template <typename T, bool VEC, int VPT, int OP, int MAXT>
 int launch_rowwise(const RowParams& p, int cta_threads, cudaStream_t stream) {
   if constexpr (VEC) {
+    if constexpr (sizeof(T) == 2 && VPT == 32 && OP == kGroupNorm && MAXT == 256) {
+      // bf16 rows of up to 4096 values with f32 weight and bias: the same threads as two rows of
+      // 16 values each, so that the parameters (four bytes from L1 per byte of x) are loaded
+      // once for two rows. layer_norm, GB/s: [65536, 4096] 3890 -> 5142, [262144, 1024] 4874 ->
+      // 5464, [2097152, 128] 5101 -> 5879. With bf16 parameters the one-row form is faster (5806
+      // against 5159 at 4096 columns), and rms_norm gains nothing either way.
+      if (!p.param_bf16 && lean_case(p, OP, VPT, Elem<T>::kVec) && p.groups <= 1 && (cta_threads / p.tpr) % 2 == 0) {
+        RowParams q = p;
+        q.tpr = 2 * p.tpr;
+        return p.n != static_cast<int64_t>(p.tpr) * VPT ? launch_rowwise_pair<T, float, 16, OP, true>(q, cta_threads, stream)
+                                                        : launch_rowwise_pair<T, float, 16, OP, false>(q, cta_threads, stream);
+      }
+    }
     if (lean_case(p, OP, VPT, Elem<T>::kVec)) {
       if (p.n == static_cast<int64_t>(p.tpr) * VPT) {
         if (p.param_bf16) return launch_rowwise_lean<T, __nv_bfloat16, VPT, OP, MAXT, false>(p, cta_threads, stream);

@@ -139,6 +139,33 @@ def test_row_lengths_that_whole_warps_cover(ops, n, dtype) -> None:
     assert checks.max_norm_rel(out.cpu(), torch.relu(ref.group_norm(xg, groups, wg, bg, 1e-5))) < bound
 
 
+@pytest.mark.parametrize("shape", [(1481, 4096), (1, 4096), (3, 2048), (777, 1024), (4099, 128), (35, 1000), (513, 768),
+                                   (129, 3072), (64, 8192), (5, 256)])
+def test_bf16_rows_with_f32_parameters(ops, shape) -> None:
+    """bf16 activations with f32 weight and bias (mixed-precision modules): layer_norm of rows
+    of up to 4096 values runs two rows per group of threads, so odd row counts, one row, a
+    tail (1000) and rows that share a warp are all here; rms_norm and wider rows take the
+    one-row form with the same operands."""
+    rows, n = shape
+    gen = torch.Generator().manual_seed(rows * 7 + n)
+    x = (torch.randn(rows, n, generator=gen) * 2 + 0.25).to(BF16)
+    w = 1 + 0.1 * torch.randn(n, generator=gen)
+    b = 0.1 * torch.randn(n, generator=gen)
+    dx, dw, db = cuda(x, w, b)
+    out = ops.layer_norm(dx, dw, db, 1e-5)
+    assert out.dtype == BF16
+    assert checks.max_norm_rel(out.cpu(), ref.layer_norm(x, w, b, 1e-5)) < 1e-2
+    # f32 parameters that are exact in bf16 against the same parameters given as bf16 (another
+    # instantiation, which adds the row up in another order: not the same bits)
+    w16, b16 = w.to(BF16), b.to(BF16)
+    exact = ops.layer_norm(dx, cuda(w16.float()), cuda(b16.float()), 1e-5)
+    assert checks.max_norm_rel(exact.cpu(), ops.layer_norm(dx, cuda(w16), cuda(b16), 1e-5).cpu()) < 1e-2
+    assert torch.equal(bits(ops.layer_norm(dx, dw, db, 1e-5)), bits(out))  # and the same bits every run
+    y = dx.clone()
+    assert torch.equal(bits(ops.layer_norm(y, dw, db, 1e-5, in_place=True)), bits(out))
+    assert checks.max_norm_rel(ops.rms_norm(dx, dw, 1e-5).cpu(), ref.rms_norm(x, w, 1e-5)) < 1e-2
+
+
 @pytest.mark.parametrize("dtype", [F32, BF16])
 @pytest.mark.parametrize("shape", [(700, 50304), (301, 32768), (150, 128256), (75, 131072), (300, 65536), (200, 40000),
                                    (40, 262144), (9, 300000)])
