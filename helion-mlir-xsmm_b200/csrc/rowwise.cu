@@ -308,9 +308,13 @@ __global__ void __launch_bounds__(MAXT) rowwise_lean_kernel(const RowParams p) {
   constexpr int NV = VPT / EPV;
   constexpr uint32_t kFillWord = OP != kSoftmax ? 0u : (sizeof(T) == 2 ? 0xff80ff80u : 0xff800000u);
   constexpr float kLog2e = 1.4426950408889634f;
-  // bf16 norms of 56 or 64 values per thread with a tail: held as f32 beside the next row's
-  // loads they spill (216 to 432 bytes per thread; layer_norm of [8388, 32000] ran at 2.3 TB/s)
-  constexpr bool LAZY = TAIL && sizeof(T) == 2 && VPT >= 56 && OP != kSoftmax;
+  // bf16 norms keep the row in its 16-bit form and widen it again in each pass where that
+  // buys resident CTAs or avoids spills: 56 or 64 values per thread with a tail (as f32 beside
+  // the next row's loads they spilt 216 to 432 bytes per thread; layer_norm of [8388, 32000]
+  // ran at 2.3 TB/s), and 32 values per thread in CTAs of 256 (80 instead of 92 registers,
+  // three CTAs per SM instead of two: layer_norm [65536, 4096] 5778 -> 6041 GB/s, [32768, 8192]
+  // 5620 -> 5881; rms_norm 6276 -> 6403).
+  constexpr bool LAZY = sizeof(T) == 2 && OP != kSoftmax && ((TAIL && VPT >= 56) || (VPT == 32 && MAXT == 256));
   __shared__ float red_a[kMaxWarpsPerRow];
   __shared__ float red_b[kMaxWarpsPerRow];
   const int tpr = p.tpr;
