@@ -100,6 +100,114 @@ __global__ void __launch_bounds__(256) row_reduce_kernel(const ReduceParams p) {
   }
 }
 
+// row_dot / matvec with R consecutive rows per group of `tpr` threads: a thread reads its
+// columns of the vector once for the R rows (the vector's loads, from L1, were two to one
+// against the row's own bytes for bf16 rows with an f32 vector, and the kernel was bound by
+// them). Each row's sum is accumulated in the same order as in row_reduce_kernel.
+template <typename T, bool VEC, int KIND, int R>
+__global__ void __launch_bounds__(256) row_dot_rows_kernel(const ReduceParams p) {
+  static_assert(KIND != 0, "row_dot and matvec only");
+  constexpr int EPV = VEC ? Elem<T>::kVec : 1;
+  __shared__ float red[8 * R];
+  const int tpr = p.tpr;
+  const int groups_per_cta = blockDim.x / tpr;
+  const int group = threadIdx.x / tpr;
+  const int t = threadIdx.x - group * tpr;
+  const int lane = threadIdx.x & 31;
+  const int warps_per_row = tpr >> 5;
+  const int warp_in_row = t >> 5;
+  const T* x = reinterpret_cast<const T*>(p.x);
+  T* out = reinterpret_cast<T*>(p.out);
+  const float* vf = reinterpret_cast<const float*>(p.v);
+  const T* vt = reinterpret_cast<const T*>(p.v);
+  const int64_t step = static_cast<int64_t>(tpr) * EPV;
+  const int64_t rows_per_cta = static_cast<int64_t>(groups_per_cta) * R;
+
+  for (int64_t base = static_cast<int64_t>(blockIdx.x) * rows_per_cta; base < p.m;
+       base += static_cast<int64_t>(gridDim.x) * rows_per_cta) {
+    const int64_t row0 = base + static_cast<int64_t>(group) * R;
+    const T* xr[R];
+#pragma unroll
+    for (int k = 0; k < R; ++k) xr[k] = x + (row0 + k < p.m ? row0 + k : p.m - 1) * p.ld;  // rows past the end re-read the last
+    float acc[R];
+#pragma unroll
+    for (int k = 0; k < R; ++k) acc[k] = 0.f;
+#pragma unroll 2
+    for (int64_t col = static_cast<int64_t>(t) * EPV; col < p.n; col += step) {
+      float xv[R][EPV];
+#pragma unroll
+      for (int k = 0; k < R; ++k) {
+        if constexpr (VEC) {
+          unpack16(ld_stream16(xr[k] + col), xv[k]);
+        } else {
+          xv[k][0] = Elem<T>::load(xr[k] + col);
+        }
+      }
+      float wv[EPV];
+      if constexpr (VEC) {
+        if (KIND == 1) {
+#pragma unroll
+          for (int q = 0; q < EPV / 4; ++q) {
+            const float4 w = __ldg(reinterpret_cast<const float4*>(vf + col) + q);
+            wv[4 * q] = w.x;
+            wv[4 * q + 1] = w.y;
+            wv[4 * q + 2] = w.z;
+            wv[4 * q + 3] = w.w;
+          }
+        } else {
+          unpack16(__ldg(reinterpret_cast<const uint4*>(vt + col)), wv);
+        }
+      } else {
+        wv[0] = KIND == 1 ? __ldg(vf + col) : Elem<T>::load(vt + col);
+      }
+#pragma unroll
+      for (int k = 0; k < R; ++k)
+#pragma unroll
+        for (int j = 0; j < EPV; ++j) acc[k] += xv[k][j] * wv[j];
+    }
+    for (int offset = (tpr < 32 ? tpr : 32) >> 1; offset > 0; offset >>= 1) {
+#pragma unroll
+      for (int k = 0; k < R; ++k) acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], offset);
+    }
+    if (warps_per_row > 1) {
+      if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < R; ++k) red[(group * warps_per_row + warp_in_row) * R + k] = acc[k];
+      }
+      __syncthreads();
+#pragma unroll
+      for (int k = 0; k < R; ++k) {
+        float r = red[group * warps_per_row * R + k];
+        for (int w = 1; w < warps_per_row; ++w) r += red[(group * warps_per_row + w) * R + k];
+        acc[k] = r;
+      }
+      __syncthreads();
+    }
+    if (t == 0) {
+#pragma unroll
+      for (int k = 0; k < R; ++k)
+        if (row0 + k < p.m) Elem<T>::store(out + row0 + k, apply_act(p.act, acc[k], p.alpha));
+    }
+  }
+}
+
+constexpr int kDotRows = 4;
+template <typename T, bool VEC, int KIND>
+int launch_row_dot_rows(const ReduceParams& p, int sm_count, cudaStream_t stream) {
+  static const int per_sm = [] {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, row_dot_rows_kernel<T, VEC, KIND, kDotRows>, 256, 0) != cudaSuccess || n < 1) {
+      cudaGetLastError();
+      n = 4;
+    }
+    return n;
+  }();
+  const int64_t wanted = ceil_div(p.m, static_cast<int64_t>(256 / p.tpr) * kDotRows);
+  const int64_t resident = static_cast<int64_t>(sm_count) * per_sm;
+  row_dot_rows_kernel<T, VEC, KIND, kDotRows><<<static_cast<unsigned>(wanted < resident ? wanted : resident), 256, 0, stream>>>(p);
+  return launched();
+}
+
 // CTAs of 256 threads that fit one SM, asked of the runtime once per instantiation: the
 // grid is persistent (rows strided by the grid), so CTAs beyond what is resident would run
 // as a second, mostly empty round (row_dot on bf16 rows needs 40 registers: six CTAs per
@@ -131,6 +239,10 @@ int launch_row_reduce(int kind, const ReduceParams& p, int64_t wanted, int sm_co
     case B200_REDUCE_ROW_SUM:
       return launch_row_reduce_kind<T, VEC, 0>(p, wanted, sm_count, stream);
     case B200_REDUCE_ROW_DOT:
+      // bf16 rows with the f32 vector: four rows per group of threads (GB/s, [65536, 4096]
+      // 5031 -> 5711, [174762, 1536] 5056 -> 5975). f32 rows lose 4-8 % that way, matvec
+      // (a vector of the rows' own type) gains and loses by shape: both stay one row per group.
+      if constexpr (sizeof(T) == 2 && VEC) return launch_row_dot_rows<T, VEC, 1>(p, sm_count, stream);
       return launch_row_reduce_kind<T, VEC, 1>(p, wanted, sm_count, stream);
     default:
       return launch_row_reduce_kind<T, VEC, 2>(p, wanted, sm_count, stream);

@@ -230,7 +230,9 @@ def test_c4_configuration(ops, dtype) -> None:
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
-@pytest.mark.parametrize("shape", [(33, 65), (16, 520), (1, 1), (7, 4096), (300, 24), (3, 70001), (2000, 8)])
+@pytest.mark.parametrize("shape", [(33, 65), (16, 520), (1, 1), (7, 4096), (300, 24), (3, 70001), (2000, 8),
+                                   # row counts around the four rows a group of threads takes in row_dot on bf16 rows
+                                   (1, 4096), (5, 1536), (1026, 64), (4099, 512), (1213, 5120)])
 def test_row_and_column_reductions(ops, shape, dtype) -> None:
     m, n = shape
     gen = torch.Generator().manual_seed(m * 7 + n)
@@ -242,6 +244,7 @@ def test_row_and_column_reductions(ops, shape, dtype) -> None:
     assert ops.row_sum(dx).shape == (m, 1) and ops.row_sum(dx).dtype == dtype
     assert checks.max_norm_rel(ops.row_sum(dx, torch.relu).cpu(), ref.row_sum(x, torch.relu)) < bound
     assert checks.max_norm_rel(ops.row_dot(dx, cuda(v)).cpu(), ref.row_dot(x, v)) < bound
+    assert torch.equal(bits(ops.row_dot(dx, cuda(v))), bits(ops.row_dot(dx, cuda(v))))
     vec = torch.randn(n, 1, generator=gen).to(dtype)
     assert checks.max_norm_rel(ops.matvec(dx, cuda(vec)).cpu(), ref.matvec(x, vec)) < bound
     col = ops.column_sum(dx)
