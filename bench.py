@@ -2,7 +2,7 @@
 other four configurations of the baseline timed beside it in the same line.
 
     python bench.py --gpus N --steps K --warmup W [--workload c2|c4|c1|c3|c5|attn|c2n|c2n_fused|kernels]
-                    [--only-main] [--impl reference]
+                    [--only-main] [--impl reference] [--row-lengths N,N,...]
 
 A step is one pass of the hot path over one batch of synthetic input. The default
 workload is the configuration the headline metric is quoted on: x [8192,4096],
@@ -606,12 +606,36 @@ class BandwidthKernels(Workload):
 
     name, metric, unit, dtype, bound = "bandwidth_kernels", "reduction / element-wise / pack HBM GB/s", "GB/s", "f32+bf16", "hbm"
     only: str | None = None  # --kernel NAME: that one kernel only (profiler captures)
+    row_lengths: list[int] | None = None  # --row-lengths: the row-wise kernels and row reductions at these lengths instead
 
     def setup(self, device: torch.device, rank: int) -> None:
         import helion_mlir_utils as ops
 
         self.ops, self.device = ops, device
         gen = torch.Generator(device=device).manual_seed(1007 + rank)
+        if self.row_lengths:
+            # softmax / layer_norm / rms_norm / row_sum / row_dot over about 0.5 GB of rows of each length
+            self.items = []
+            for n in self.row_lengths:
+                for dtype, name, size in ((torch.float32, "f32", 4), (torch.bfloat16, "bf16", 2)):
+                    m = max(1, (1 << 29) // (n * size))
+                    x = torch.randn(m, n, generator=gen, device=device).to(dtype)
+                    g, b = torch.randn(n, device=device).to(dtype), torch.randn(n, device=device).to(dtype)
+                    v = torch.randn(n, device=device)
+                    both, once = 2.0 * m * n * size, 1.0 * m * n * size
+                    tag = f"{name}_{m}x{n}"
+                    self.items += [
+                        (f"softmax_{tag}", both, lambda x=x: ops.softmax(x)),
+                        (f"layer_norm_{tag}", both, lambda x=x, g=g, b=b: ops.layer_norm(x, g, b, 1e-5)),
+                        (f"rms_norm_{tag}", both, lambda x=x, g=g: ops.rms_norm(x, g, 1e-5)),
+                        (f"row_sum_{tag}", once, lambda x=x: ops.row_sum(x)),
+                        (f"row_dot_{tag}", once, lambda x=x, v=v: ops.row_dot(x, v)),
+                    ]
+            if self.only:
+                self.items = [item for item in self.items if item[0] == self.only]
+                if not self.items:
+                    raise SystemExit(f"--kernel {self.only}: no such kernel in this workload")
+            return
         m, n = 32768, 4096
         x32 = torch.randn(m, n, generator=gen, device=device)
         x16 = x32.bfloat16()
@@ -1018,6 +1042,9 @@ def main() -> None:
     parser.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     parser.add_argument("--rows", type=int, default=0, help="rows per GPU of the c2/c4 workloads, heads per GPU of attn, batches per GPU of c5 (default: the configuration's; smaller sizes are for profiler captures, not for reported numbers)")
     parser.add_argument("--kernel", default=None, help="kernels workload: run this one kernel only (profiler captures)")
+    parser.add_argument("--row-lengths", default=None,
+                        help="kernels workload: time softmax, layer_norm, rms_norm, row_sum and row_dot over rows of these "
+                             "lengths (comma separated) in f32 and bf16 instead of the fixed list")
     parser.add_argument("--only-main", action="store_true", help="skip the blocks of the other configurations, the sustained leg and the linear() leg")
     parser.add_argument("--via-linear", action="store_true", help="c2: time linear(x, layer, F.gelu, cache) as the main step")
     parser.add_argument("--no-cpu-baseline", action="store_true")
@@ -1035,6 +1062,8 @@ def main() -> None:
                 break
     if isinstance(workload, BandwidthKernels):
         workload.only = args.kernel
+        if args.row_lengths:
+            workload.row_lengths = [int(v) for v in args.row_lengths.split(",") if v]
     if args.via_linear and isinstance(workload, LinearGelu):
         workload.via_linear = True
     if args.impl == "reference":
