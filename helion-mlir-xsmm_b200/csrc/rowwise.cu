@@ -917,7 +917,7 @@ int launch_rowwise_pair(const RowParams& p, int cta_threads, cudaStream_t stream
 struct RowCover {
   int tpr, vpt;
 };
-inline RowCover row_cover(int64_t n, int elem_bytes, bool wide_tail) {
+inline RowCover row_cover(int64_t n, int elem_bytes) {
   const int epv = 16 / elem_bytes;
   const int order_f32[4] = {16, 24, 32, 8}, order_bf16[5] = {32, 64, 24, 16, 8};
   const int* order = elem_bytes == 2 ? order_bf16 : order_f32;
@@ -933,9 +933,8 @@ inline RowCover row_cover(int64_t n, int elem_bytes, bool wide_tail) {
         tpr = n / vpt;
         if (tpr % 32) continue;
       } else {
-        // 64 values with a tail fit 128 registers for softmax only: layer_norm spilt
-        // 432 bytes and ran [24385, 11008] bf16 at 2.2 TB/s (softmax: 5.8)
-        if (vpt == 64 && !wide_tail) continue;
+        // (64 bf16 values with a tail: the norms keep the row in 16 bits there, see LAZY; held
+        // as f32 they spilt and layer_norm of [24385, 11008] ran at 2.2 TB/s, now 4.9)
         tpr = ceil_div(ceil_div(n, static_cast<int64_t>(vpt)), int64_t(32)) * 32;
         if (tpr * (vpt - epv) >= n) continue;  // no thread's last vector starts within the row: fewer values do
       }
@@ -1066,7 +1065,7 @@ int run_rowwise(RowParams p, cudaStream_t stream) {
   // [8192, 16384]: 4.45 TB/s), two CTAs of 256 x 64 keep 64 KB (5.84 TB/s).
   const bool exact = p.n == static_cast<int64_t>(tpr) * vpt;
   if (vec && tpr >= 32 && (!exact || (sizeof(T) == 2 && tpr == 512 && vpt == 32))) {
-    const RowCover cover = row_cover(p.n, sizeof(T), OP == kSoftmax);
+    const RowCover cover = row_cover(p.n, sizeof(T));
     if (cover.tpr) {
       tpr = cover.tpr;
       vpt = cover.vpt;
