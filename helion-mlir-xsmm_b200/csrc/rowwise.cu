@@ -872,9 +872,10 @@ int launch_rowwise_lean(const RowParams& p, int cta_threads, cudaStream_t stream
   // lose: [65536, 4096] 6193 / 5779 / 6322 -> 6001 / 5482 / 6355). One group per CTA fetches
   // nothing ahead and 16 or 32 groups approach the strided form again.
   // (bf16 rows of 768 values, 24 per thread, lose too: layer_norm 6188 -> 5536.) Two groups
-  // where three CTAs are resident, four where two are; a single resident CTA strides.
+  // where three CTAs are resident, four where two are and for group_norm (f32 layer_norm of
+  // 4096 columns: 6020 with two, 6320 with four); a single resident CTA strides.
   const bool chunked = (sizeof(T) == 4 || (p.tpr <= 32 && VPT == 32)) && per_sm >= 2;
-  const int chunk = chunked ? (per_sm >= 3 ? 2 : 4) : 0;
+  const int chunk = chunked ? (per_sm >= 3 && OP != kGroupNorm ? 2 : 4) : 0;
   if (chunk > 0 && wanted > resident * chunk) {
     RowParams q = p;
     q.part = chunk;
