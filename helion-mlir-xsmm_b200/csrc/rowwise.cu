@@ -13,6 +13,8 @@
 // (lines 52-72: multiply by the reciprocal), GroupNorm = two-pass mean then
 // biased variance of the centred values (lines 114-122), everything in f32 with
 // one rounding to the output type.
+#include <cstdio>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -958,6 +960,20 @@ inline RowCover row_cover(int64_t n, int elem_bytes) {
   return RowCover{0, 0};
 }
 
+// Threads per row, values per thread and CTA size for rows of `n` elements of `elem_bytes`
+// (host arithmetic only; `vec`: 16-byte accesses are possible). two_pass: the row does not fit
+// the registers of 512 threads and takes the one-CTA-per-row kernel.
+struct RowPlan {
+  int tpr, vpt, cta_threads;
+  bool two_pass;
+};
+
+// Whether the two-rows-per-group form takes a layer_norm (see launch_rowwise).
+inline bool pair_case(int elem_bytes, int op, const RowPlan& plan, bool param_bf16, int64_t groups) {
+  return elem_bytes == 2 && op == kGroupNorm && plan.vpt == 32 && plan.cta_threads <= 256 && !param_bf16 && groups <= 1 &&
+         (plan.cta_threads / plan.tpr) % 2 == 0;
+}
+
 // Whether the lean kernel applies: whole vectors, vector parameters, plain affine form.
 inline bool lean_case(const RowParams& p, int op, int vpt, int epv) {
   if (p.n > static_cast<int64_t>(p.tpr) * vpt || vpt % epv) return false;
@@ -976,7 +992,8 @@ int launch_rowwise(const RowParams& p, int cta_threads, cudaStream_t stream) {
       // once for two rows. layer_norm, GB/s: [65536, 4096] 3890 -> 5142, [262144, 1024] 4874 ->
       // 5464, [2097152, 128] 5101 -> 5879. With bf16 parameters the one-row form is faster (5806
       // against 5159 at 4096 columns), and rms_norm gains nothing either way.
-      if (!p.param_bf16 && lean_case(p, OP, VPT, Elem<T>::kVec) && p.groups <= 1 && (cta_threads / p.tpr) % 2 == 0) {
+      if (lean_case(p, OP, VPT, Elem<T>::kVec) &&
+          pair_case(sizeof(T), OP, RowPlan{p.tpr, VPT, cta_threads, false}, p.param_bf16 != 0, p.groups)) {
         RowParams q = p;
         q.tpr = 2 * p.tpr;
         return p.n != static_cast<int64_t>(p.tpr) * VPT ? launch_rowwise_pair<T, float, 16, OP, true>(q, cta_threads, stream)
@@ -1022,20 +1039,15 @@ int dispatch_vpt(const RowParams& p, int vpt, int cta_threads, cudaStream_t stre
   }
 }
 
-template <typename T, int OP>
-int run_rowwise(RowParams p, cudaStream_t stream) {
-  if (p.rows == 0 || p.n == 0) return finish(0);
-  const DeviceInfo& dev = device_info();
-  if (dev.sm_count == 0) return refuse(B200_E_DEVICE);
-  const int kvec = Elem<T>::kVec;
-  const bool vec = (p.n % kvec == 0) && (p.ld % kvec == 0) && aligned(p.x, 16) && aligned(p.y, 16);
-  const int64_t units = vec ? p.n / kvec : p.n;  // accesses per row
+inline RowPlan plan_rows(int64_t n, int elem_bytes, bool vec) {
+  const int kvec = 16 / elem_bytes;
+  const int64_t units = vec ? n / kvec : n;  // accesses per row
   const int per_unit = vec ? kvec : 1;
   // Threads per row: up to 256 at 16 values per thread, then 32 values per
   // thread, then wider CTAs (which are held to 64 registers per thread).
   // (bf16 rows aim at 32 values per thread from the start: 64 bytes of loads in flight per
   // thread, as for f32, and half as many warps to reduce across)
-  const int first = sizeof(T) == 2 && vec ? 32 : 16;
+  const int first = elem_bytes == 2 && vec ? 32 : 16;
   const int units16 = first / per_unit > 0 ? first / per_unit : 1, units32 = 32 / per_unit;
   // Rows of less than a warp's worth of values share a warp (down to 4 threads per row).
   int tpr = 4;
@@ -1047,36 +1059,46 @@ int run_rowwise(RowParams p, cudaStream_t stream) {
   // values each; longer rows go through the two-pass kernel. Measured at 32768 columns:
   // bf16 5.5 TB/s in registers against 3.9 for the two passes; f32 4.0 (64 values spill)
   // against 5.0; a 1024-thread CTA, held to 64 registers, 3.7.
-  if (vpt_needed > (sizeof(T) == 2 ? 64 : 32)) {
-    const int64_t resident = static_cast<int64_t>(dev.sm_count) * 2;
-    const unsigned grid = static_cast<unsigned>(p.rows < resident ? p.rows : resident);
-    p.tpr = 1024;
-    p.param_vec = vec && aligned(p.weight, 16) && aligned(p.bias, 16) && aligned(p.extra, 16);
-    if (vec)
-      rowwise_long_kernel<T, OP, true><<<grid, 1024, 0, stream>>>(p);
-    else
-      rowwise_long_kernel<T, OP, false><<<grid, 1024, 0, stream>>>(p);
-    return launched();
-  }
+  if (vpt_needed > (elem_bytes == 2 ? 64 : 32)) return RowPlan{1024, 0, 1024, true};
   int vpt = vpt_needed <= 8 ? 8 : (vpt_needed <= 16 ? 16 : (vpt_needed <= 32 ? 32 : 64));
-  if (sizeof(T) == 2 && vec && vpt == 64) vpt = static_cast<int>(round_up(vpt_needed, 8));  // 40, 48, 56 or 64
+  if (elem_bytes == 2 && vec && vpt == 64) vpt = static_cast<int>(round_up(vpt_needed, 8));  // 40, 48, 56 or 64
   int cta_threads = tpr > 256 ? tpr : 256;
   // The power-of-two cover above is kept where it is exact, but for bf16 rows of 512 threads
   // x 32 values: one such CTA fits an SM and keeps 32 KB in flight (layer_norm of
   // [8192, 16384]: 4.45 TB/s), two CTAs of 256 x 64 keep 64 KB (5.84 TB/s).
-  const bool exact = p.n == static_cast<int64_t>(tpr) * vpt;
-  if (vec && tpr >= 32 && (!exact || (sizeof(T) == 2 && tpr == 512 && vpt == 32))) {
-    const RowCover cover = row_cover(p.n, sizeof(T));
+  const bool exact = n == static_cast<int64_t>(tpr) * vpt;
+  if (vec && tpr >= 32 && (!exact || (elem_bytes == 2 && tpr == 512 && vpt == 32))) {
+    const RowCover cover = row_cover(n, elem_bytes);
     if (cover.tpr) {
       tpr = cover.tpr;
       vpt = cover.vpt;
       cta_threads = tpr >= 256 ? tpr : tpr * (256 / tpr);
     }
   }
-  p.tpr = tpr;
+  return RowPlan{tpr, vpt, cta_threads, false};
+}
+
+template <typename T, int OP>
+int run_rowwise(RowParams p, cudaStream_t stream) {
+  if (p.rows == 0 || p.n == 0) return finish(0);
+  const DeviceInfo& dev = device_info();
+  if (dev.sm_count == 0) return refuse(B200_E_DEVICE);
+  const int kvec = Elem<T>::kVec;
+  const bool vec = (p.n % kvec == 0) && (p.ld % kvec == 0) && aligned(p.x, 16) && aligned(p.y, 16);
+  const RowPlan plan = plan_rows(p.n, sizeof(T), vec);
   p.param_vec = vec && aligned(p.weight, 16) && aligned(p.bias, 16) && aligned(p.extra, 16);
-  if (vec) return dispatch_vpt<T, true, OP>(p, vpt, cta_threads, stream);
-  return dispatch_vpt<T, false, OP>(p, vpt, cta_threads, stream);
+  p.tpr = plan.tpr;
+  if (plan.two_pass) {
+    const int64_t resident = static_cast<int64_t>(dev.sm_count) * 2;
+    const unsigned grid = static_cast<unsigned>(p.rows < resident ? p.rows : resident);
+    if (vec)
+      rowwise_long_kernel<T, OP, true><<<grid, 1024, 0, stream>>>(p);
+    else
+      rowwise_long_kernel<T, OP, false><<<grid, 1024, 0, stream>>>(p);
+    return launched();
+  }
+  if (vec) return dispatch_vpt<T, true, OP>(p, plan.vpt, plan.cta_threads, stream);
+  return dispatch_vpt<T, false, OP>(p, plan.vpt, plan.cta_threads, stream);
 }
 
 template <int OP>
@@ -1133,6 +1155,47 @@ extern "C" int b200_group_norm(int32_t dtype, int32_t param_dtype, const void* x
   p.alpha = alpha;
   p.eps = eps;
   return run_rowwise_dtype<kGroupNorm>(dtype, p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200_rowwise_explain(int32_t op, int32_t dtype, int32_t param_dtype, const void* x, const void* y,
+                                    int64_t n, int64_t ld, int64_t groups, const void* weight, const void* bias,
+                                    const void* extra, int32_t extra_op, int32_t act, char* out, size_t out_len) {
+  if (!out || out_len == 0) return B200_E_NULL;
+  out[0] = 0;
+  if (op < kSoftmax || op > kRmsNorm) return B200_E_ARG;
+  if (!valid_dtype(dtype) || !valid_dtype(param_dtype)) return B200_E_DTYPE;
+  if (n < 1 || ld < n) return B200_E_SHAPE;
+  const int size = static_cast<int>(dtype_size(dtype)), kvec = 16 / size;
+  const bool vec = (n % kvec == 0) && (ld % kvec == 0) && aligned(x, 16) && aligned(y, 16);
+  const RowPlan plan = plan_rows(n, size, vec);
+  if (plan.two_pass) {
+    snprintf(out, out_len, "rowwise_long_kernel: one CTA of 1024 threads per row, %d sweeps, %s accesses",
+             op == kGroupNorm ? 3 : 2, vec ? "16-byte" : "element");
+    return 0;
+  }
+  RowParams p{};
+  p.n = n;
+  p.tpr = plan.tpr;
+  p.groups = groups < 1 ? 1 : groups;
+  p.weight = weight;
+  p.bias = bias;
+  p.extra_op = extra_op;
+  p.act = act;
+  p.param_bf16 = param_dtype == B200_BF16;
+  p.param_vec = vec && aligned(weight, 16) && aligned(bias, 16) && aligned(extra, 16);
+  const bool lean = vec && lean_case(p, op, plan.vpt, kvec);
+  const bool tail = n != static_cast<int64_t>(plan.tpr) * plan.vpt;
+  if (lean && pair_case(size, op, plan, p.param_bf16 != 0, p.groups)) {
+    snprintf(out, out_len, "rowwise_pair_kernel: two rows per group of %d threads x 16 values, %d groups per CTA of %d threads%s",
+             2 * plan.tpr, plan.cta_threads / (2 * plan.tpr), plan.cta_threads, tail ? ", tail" : "");
+    return 0;
+  }
+  const bool lazy = lean && size == 2 && op != kSoftmax &&
+                    ((tail && plan.vpt >= 56) || (plan.vpt == 32 && plan.cta_threads <= 256));
+  snprintf(out, out_len, "%s: %d threads x %d values per row, %d rows per CTA of %d threads%s%s",
+           lean ? "rowwise_lean_kernel" : (vec ? "rowwise_kernel (masked)" : "rowwise_kernel (masked, element accesses)"), plan.tpr,
+           plan.vpt, plan.cta_threads / plan.tpr, plan.cta_threads, lean && tail ? ", tail" : "", lazy ? ", row kept in 16 bits" : "");
+  return 0;
 }
 
 extern "C" int b200_rms_norm(int32_t dtype, int32_t param_dtype, const void* x, void* y, int64_t m, int64_t n,

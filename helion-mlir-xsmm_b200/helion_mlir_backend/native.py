@@ -176,6 +176,11 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
         ],
     ),
     "b200_rms_norm": (c_int, [c_int32, c_int32, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_float, c_void_p]),
+    "b200_rowwise_explain": (
+        c_int,
+        [c_int32, c_int32, c_int32, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int32,
+         c_int32, ctypes.c_char_p, c_size_t],
+    ),
     "b200_row_reduce": (
         c_int,
         [c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int32, c_float, c_void_p],

@@ -15,8 +15,11 @@ from typing import Callable
 import torch
 from torch import Tensor
 
+import ctypes
+
 from helion_mlir_backend import native
 from helion_mlir_backend import output_pool
+from helion_mlir_backend.call_trace import CallExplanation
 
 from . import epilogues
 
@@ -194,3 +197,67 @@ def rms_norm(x: Tensor, weight: Tensor | None = None, eps: float = 1e-5, in_plac
         )
     native.check("b200_rms_norm", code)
     return out
+
+
+# --------------------------------------------------------------------------- explain()
+# What a call would launch (kernel family, threads and values per thread per row, rows per
+# CTA, tail, row kept in 16 bits, two rows per group): host arithmetic in the library
+# (`b200_rowwise_explain`), so it also answers for CPU tensors of the same shape and type.
+
+_OP_SOFTMAX, _OP_GROUP_NORM, _OP_RMS_NORM = 0, 1, 2
+
+
+def _param_dtype(params: list[Tensor]) -> torch.dtype:
+    if params and all(t.dtype == torch.bfloat16 for t in params):
+        return torch.bfloat16
+    return torch.float32
+
+
+def _explain_rows(op: int, x: Tensor, n: int, groups: int, weight: Tensor | None, bias: Tensor | None,
+                  extra: Tensor | None = None, extra_op: int = native.NORM_EXTRA_NONE,
+                  act: int = native.ACT_IDENTITY) -> CallExplanation:
+    if x.dim() != 2 or x.dtype not in (torch.float32, torch.bfloat16):
+        return CallExplanation(False, "", f"expects a 2-D f32 or bf16 tensor, got {tuple(x.shape)} {x.dtype}")
+    x = x.contiguous()
+    param_dtype = _param_dtype([t for t in (weight, bias, extra) if t is not None])
+    held = [None if t is None else t.to(param_dtype).contiguous() for t in (weight, bias, extra)]
+    buf = ctypes.create_string_buffer(256)
+    code = native.module().b200_rowwise_explain(
+        op, native.dtype_code(x.dtype), native.dtype_code(param_dtype), x.data_ptr(), x.data_ptr(), n, n, groups,
+        native.ptr(held[0]), native.ptr(held[1]), native.ptr(held[2]), extra_op, act, buf, len(buf))
+    text = buf.value.decode()
+    return CallExplanation(code == 0, text, None if code == 0 else native.strerror(code))
+
+
+def _explain_softmax(x: Tensor, in_place: bool = False) -> CallExplanation:
+    return _explain_rows(_OP_SOFTMAX, x, int(x.shape[-1]), 1, None, None)
+
+
+def _explain_group_norm(x: Tensor, num_groups: int, weight: Tensor | None, bias: Tensor | None, eps: float = 1e-5,
+                        epilogue: Callable[[Tensor, Tensor], Tensor] = _second_operand, extra: Tensor | None = None,
+                        in_place: bool = False) -> CallExplanation:
+    extra_op = _EXTRA_OPS.get(epilogue, native.NORM_EXTRA_NONE)
+    act = native.ACT_IDENTITY
+    if epilogue not in _EXTRA_OPS and getattr(epilogue, "__name__", None) != "_second_operand":
+        unary = epilogues.resolve(epilogue)
+        if unary is None:
+            return CallExplanation(True, "group_norm in f32 through the row-wise kernel, then the epilogue as its own device pass")
+        act = unary[0]
+    if extra_op != native.NORM_EXTRA_NONE and extra is None:
+        extra = weight
+    return _explain_rows(_OP_GROUP_NORM, x, int(x.shape[-1]) // num_groups, num_groups, weight, bias, extra, extra_op, act)
+
+
+def _explain_layer_norm(x: Tensor, weight: Tensor | None = None, bias: Tensor | None = None, eps: float = 1e-5,
+                        in_place: bool = False) -> CallExplanation:
+    return _explain_rows(_OP_GROUP_NORM, x, int(x.shape[-1]), 1, weight, bias)
+
+
+def _explain_rms_norm(x: Tensor, weight: Tensor | None = None, eps: float = 1e-5, in_place: bool = False) -> CallExplanation:
+    return _explain_rows(_OP_RMS_NORM, x, int(x.shape[-1]), 1, weight, None)
+
+
+softmax.explain = _explain_softmax  # type: ignore[attr-defined]
+group_norm.explain = _explain_group_norm  # type: ignore[attr-defined]
+layer_norm.explain = _explain_layer_norm  # type: ignore[attr-defined]
+rms_norm.explain = _explain_rms_norm  # type: ignore[attr-defined]

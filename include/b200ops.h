@@ -216,6 +216,16 @@ int b200_group_norm(int32_t dtype, int32_t param_dtype, const void* x, void* y, 
 int b200_rms_norm(int32_t dtype, int32_t param_dtype, const void* x, void* y, int64_t m, int64_t n,
                   const void* weight, float eps, void* stream);
 
+/* What b200_softmax (op 0), b200_group_norm (1) or b200_rms_norm (2) would launch for rows of
+ * `n` elements `ld` apart with these operands: the kernel family, threads and values per
+ * thread per row, rows per CTA, whether the row has a tail, is kept in 16 bits, or is taken
+ * two rows at a time. Host arithmetic only (needs no GPU; the pointers are only tested for
+ * alignment and presence). The counterpart of explain() for the row-wise operators
+ * (_compiler/call_trace.py:84-217 reports the path a call takes). Returns 0 or a refusal code. */
+int b200_rowwise_explain(int32_t op, int32_t dtype, int32_t param_dtype, const void* x, const void* y, int64_t n,
+                         int64_t ld, int64_t groups, const void* weight, const void* bias, const void* extra,
+                         int32_t extra_op, int32_t act, char* out, size_t out_len);
+
 /* Row reductions of x [M,N] (ld = row stride) into out [M] of `dtype`:
  *   B200_REDUCE_ROW_SUM:  act(sum_n x[m,n])                 reduction.py:79-121
  *   B200_REDUCE_ROW_DOT:  act(sum_n x[m,n] * v[n]), v f32   reduction.py:166-212
