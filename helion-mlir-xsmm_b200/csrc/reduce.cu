@@ -7,6 +7,8 @@
 // helion_mlir_utils/reduction.py.
 #include <mutex>
 
+#include <cstdio>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -249,6 +251,13 @@ int launch_row_reduce(int kind, const ReduceParams& p, int64_t wanted, int sm_co
   }
 }
 
+// Threads per row of the row reductions for rows of `units` accesses (see run_row_reduce).
+inline int row_reduce_threads(int64_t units) {
+  int tpr = 4;
+  while (tpr < 256 && static_cast<int64_t>(tpr) * 8 < units) tpr <<= 1;
+  return tpr;
+}
+
 template <typename T>
 int run_row_reduce(int kind, ReduceParams p, cudaStream_t stream) {
   const DeviceInfo& dev = device_info();
@@ -261,8 +270,7 @@ int run_row_reduce(int kind, ReduceParams p, cudaStream_t stream) {
   // threads: half the loads in flight per thread and twice the warps to add up per row
   // (GB/s, [65536, 4096] bf16: row_sum 6184 -> 6748, row_dot 4434 -> 5036, matvec 5149 -> 6151;
   // rows of 1536, 3072 and 6144 bf16 values, three units per thread before: row_sum 4.7 -> 6.4-6.6).
-  int tpr = 4;
-  while (tpr < 256 && static_cast<int64_t>(tpr) * 8 < units) tpr <<= 1;
+  const int tpr = row_reduce_threads(units);
   p.tpr = tpr;
   const int rows_per_cta = 256 / tpr;
   const int64_t wanted = ceil_div(p.m, rows_per_cta);
@@ -515,6 +523,39 @@ extern "C" int b200_row_reduce(int32_t kind, int32_t dtype, const void* x, const
   p.alpha = alpha;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return dtype == B200_F32 ? run_row_reduce<float>(kind, p, s) : run_row_reduce<__nv_bfloat16>(kind, p, s);
+}
+
+extern "C" int b200_reduce_explain(int32_t kind, int32_t dtype, const void* x, const void* v, int64_t m, int64_t n,
+                                   int64_t ld, char* out, size_t out_len) {
+  if (!out || out_len == 0) return B200_E_NULL;
+  out[0] = 0;
+  if (!valid_dtype(dtype)) return B200_E_DTYPE;
+  constexpr int kColumnSum = 3;  // beside the B200_REDUCE_* kinds of the row reductions
+  if (kind < 0 || kind > kColumnSum) return B200_E_ARG;
+  if (m < 1 || n < 1 || ld < n) return B200_E_SHAPE;
+  const int size = static_cast<int>(dtype_size(dtype)), kvec = 16 / size;
+  if (kind == kColumnSum) {
+    const int cpt = column_cpt(dtype, x, n, ld);
+    const ColPlan plan = column_plan(m, n, cpt);
+    const long long strip = static_cast<long long>(cpt) << plan.tpr_log2;
+    if (plan.chunks > 1)
+      snprintf(out, out_len,
+               "column_partial_kernel: %lld strips of %lld columns (%d per thread) x %lld chunks of %lld rows, then "
+               "column_final_kernel adds the chunks in order (%zu bytes of scratch)",
+               static_cast<long long>(plan.col_tiles), strip, cpt, static_cast<long long>(plan.chunks),
+               static_cast<long long>(plan.rows_per_chunk), static_cast<size_t>(plan.chunks) * n * sizeof(float));
+    else
+      snprintf(out, out_len, "column_partial_kernel: %lld strips of %lld columns (%d per thread), one chunk of %lld rows",
+               static_cast<long long>(plan.col_tiles), strip, cpt, static_cast<long long>(plan.rows_per_chunk));
+    return 0;
+  }
+  const bool vec = (n % kvec == 0) && (ld % kvec == 0) && aligned(x, 16) && (!v || aligned(v, 16));
+  const int tpr = row_reduce_threads(vec ? n / kvec : n);
+  const bool four = kind == B200_REDUCE_ROW_DOT && size == 2 && vec;
+  snprintf(out, out_len, "%s: %d threads per row, %d rows per CTA of 256 threads, %s accesses",
+           four ? "row_dot_rows_kernel (four rows per group of threads)" : "row_reduce_kernel", tpr,
+           (256 / tpr) * (four ? kDotRows : 1), vec ? "16-byte" : "element");
+  return 0;
 }
 
 extern "C" size_t b200_column_sum_workspace_bytes(int64_t m, int64_t n) { return column_sum_workspace(m, n); }

@@ -185,6 +185,8 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
         c_int,
         [c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int32, c_float, c_void_p],
     ),
+    "b200_reduce_explain": (
+        c_int, [c_int32, c_int32, c_void_p, c_void_p, c_int64, c_int64, c_int64, ctypes.c_char_p, c_size_t]),
     "b200_column_sum_workspace_bytes": (c_size_t, [c_int64, c_int64]),
     "b200_column_sum": (c_int, [c_int32, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_size_t, c_void_p]),
     "b200_column_sum_static": (c_int, [c_int32, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),

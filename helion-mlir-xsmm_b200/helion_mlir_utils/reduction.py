@@ -110,3 +110,32 @@ def column_sum(x: Tensor) -> Tensor:
         )
     native.check("b200_column_sum", code)
     return out
+
+
+# --------------------------------------------------------------------------- explain()
+# What a call would launch: host arithmetic in the library (`b200_reduce_explain`), so it
+# also answers for CPU tensors of the same shape and type.
+
+_KIND_ROW_SUM, _KIND_ROW_DOT, _KIND_MATVEC, _KIND_COLUMN_SUM = 0, 1, 2, 3
+
+
+def _explain_reduction(kind: int, x: Tensor, v: Tensor | None):
+    import ctypes
+
+    from helion_mlir_backend.call_trace import CallExplanation
+
+    if x.dim() != 2 or x.dtype not in (torch.float32, torch.bfloat16) or x.numel() == 0:
+        return CallExplanation(False, "", f"expects a non-empty 2-D f32 or bf16 tensor, got {tuple(x.shape)} {x.dtype}")
+    x = x.contiguous()
+    m, n = map(int, x.shape)
+    if v is not None:
+        v = v.reshape(-1).to(torch.float32 if kind == _KIND_ROW_DOT else x.dtype).contiguous()
+    buf = ctypes.create_string_buffer(320)
+    code = native.module().b200_reduce_explain(kind, native.dtype_code(x.dtype), x.data_ptr(), native.ptr(v), m, n, n, buf, len(buf))
+    return CallExplanation(code == 0, buf.value.decode(), None if code == 0 else native.strerror(code))
+
+
+row_sum.explain = lambda x, epilogue=identity_epilogue: _explain_reduction(_KIND_ROW_SUM, x, None)  # type: ignore[attr-defined]
+row_dot.explain = lambda x, v, epilogue=identity_epilogue: _explain_reduction(_KIND_ROW_DOT, x, v)  # type: ignore[attr-defined]
+matvec.explain = lambda a, b: _explain_reduction(_KIND_MATVEC, a, b)  # type: ignore[attr-defined]
+column_sum.explain = lambda x: _explain_reduction(_KIND_COLUMN_SUM, x, None)  # type: ignore[attr-defined]

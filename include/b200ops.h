@@ -234,6 +234,14 @@ enum { B200_REDUCE_ROW_SUM = 0, B200_REDUCE_ROW_DOT = 1, B200_REDUCE_MATVEC = 2 
 int b200_row_reduce(int32_t kind, int32_t dtype, const void* x, const void* v, void* out, int64_t m,
                     int64_t n, int64_t ld, int32_t act, float alpha, void* stream);
 
+/* What b200_row_reduce (kind B200_REDUCE_*) or b200_column_sum (kind 3) would launch for an
+ * [m, n] operand with rows `ld` apart: threads per row and rows per CTA, or the strips, chunks
+ * and scratch of the column sum. Host arithmetic only (needs no GPU; the pointers are only
+ * tested for alignment). Counterpart of explain() (_compiler/call_trace.py:84-217) for the
+ * reductions. Returns 0 or a refusal code. */
+int b200_reduce_explain(int32_t kind, int32_t dtype, const void* x, const void* v, int64_t m, int64_t n, int64_t ld,
+                        char* out, size_t out_len);
+
 /* Column sums of x [M,N] into out [N] f32, fixed summation order (no atomics).
  * `workspace` holds b200_column_sum_workspace_bytes(m, n) bytes of partial sums
  * (may be NULL when that is 0). Replaces _column_sum_kernel (reduction.py:124-163). */

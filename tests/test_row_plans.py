@@ -1,8 +1,8 @@
-"""Launch plans of the row-wise operators, pinned as the reference pins its tile heuristics
+"""Launch plans of the row-wise operators and the reductions, pinned as the reference pins its tile heuristics
 (exact values: ``tests/test_cpu_utils_prepacked.py:392-510`` for ``vnni_panel`` and
-``whole_row_tiles``). ``explain()`` of softmax / layer_norm / rms_norm / group_norm is host
-arithmetic in the library (``b200_rowwise_explain``), so it runs without a GPU on CPU tensors
-of the same shape and type."""
+``whole_row_tiles``). ``explain()`` of softmax / layer_norm / rms_norm / group_norm and of row_sum / row_dot / matvec /
+column_sum is host arithmetic in the library (``b200_rowwise_explain``, ``b200_reduce_explain``),
+so it runs without a GPU on CPU tensors of the same shape and type."""
 
 from __future__ import annotations
 
@@ -78,3 +78,53 @@ def test_explain_goes_through_the_backend_entry(ops) -> None:
     assert str(explain(ops.softmax, torch.zeros(4, 4096))) == "native: " + PLANS[("softmax", 4096, F32, None)]
     refused = ops.softmax.explain(torch.zeros(4, 8, dtype=torch.float64))
     assert not refused.native and "f32 or bf16" in str(refused)
+
+
+REDUCTIONS = {
+    # (m, n, dtype): (row_sum, row_dot with an f32 vector, matvec)
+    (64, 4096, F32): ("row_reduce_kernel: 128 threads per row, 2 rows per CTA of 256 threads, 16-byte accesses",) * 3,
+    (64, 4096, BF16): (
+        "row_reduce_kernel: 64 threads per row, 4 rows per CTA of 256 threads, 16-byte accesses",
+        "row_dot_rows_kernel (four rows per group of threads): 64 threads per row, 16 rows per CTA of 256 threads, 16-byte accesses",
+        "row_reduce_kernel: 64 threads per row, 4 rows per CTA of 256 threads, 16-byte accesses",
+    ),
+    (64, 64, BF16): (
+        "row_reduce_kernel: 4 threads per row, 64 rows per CTA of 256 threads, 16-byte accesses",
+        "row_dot_rows_kernel (four rows per group of threads): 4 threads per row, 256 rows per CTA of 256 threads, 16-byte accesses",
+        "row_reduce_kernel: 4 threads per row, 64 rows per CTA of 256 threads, 16-byte accesses",
+    ),
+    (64, 333, F32): ("row_reduce_kernel: 64 threads per row, 4 rows per CTA of 256 threads, element accesses",) * 3,
+    (64, 12288, F32): ("row_reduce_kernel: 256 threads per row, 1 rows per CTA of 256 threads, 16-byte accesses",) * 3,
+}
+
+COLUMN_SUMS = {
+    (32768, 4096, BF16): "column_partial_kernel: 8 strips of 512 columns (8 per thread) x 128 chunks of 256 rows, then "
+                         "column_final_kernel adds the chunks in order (2097152 bytes of scratch)",
+    (1 << 20, 64, BF16): "column_partial_kernel: 1 strips of 64 columns (8 per thread) x 1024 chunks of 1024 rows, then "
+                         "column_final_kernel adds the chunks in order (262144 bytes of scratch)",
+    (1, 4096, F32): "column_partial_kernel: 8 strips of 512 columns (4 per thread), one chunk of 1 rows",
+    (100, 333, F32): "column_partial_kernel: 3 strips of 128 columns (1 per thread), one chunk of 100 rows",
+}
+
+
+@pytest.mark.parametrize("shape", list(REDUCTIONS), ids=[f"{m}x{n}-{str(dt)[6:]}" for m, n, dt in REDUCTIONS])
+def test_row_reduction_plans(ops, shape) -> None:
+    m, n, dtype = shape
+    x = torch.zeros(m, n, dtype=dtype)
+    got = (ops.row_sum.explain(x).kernel, ops.row_dot.explain(x, torch.zeros(n)).kernel,
+           ops.matvec.explain(x, torch.zeros(n, 1, dtype=dtype)).kernel)
+    assert got == REDUCTIONS[shape]
+
+
+@pytest.mark.parametrize("shape", list(COLUMN_SUMS), ids=[f"{m}x{n}-{str(dt)[6:]}" for m, n, dt in COLUMN_SUMS])
+def test_column_sum_plans(ops, shape) -> None:
+    """The scratch the plan names is what ``b200_column_sum_workspace_bytes`` asks for at most
+    (the query does not know the operand's alignment and takes the largest of the three vector widths)."""
+    from helion_mlir_backend import native
+
+    m, n, dtype = shape
+    plan = ops.column_sum.explain(torch.zeros(m, n, dtype=dtype))
+    assert plan.native and plan.kernel == COLUMN_SUMS[shape]
+    need = int(native.module().b200_column_sum_workspace_bytes(m, n))
+    if "bytes of scratch" in plan.kernel:
+        assert int(plan.kernel.split("(")[-1].split(" bytes")[0]) <= need
